@@ -19,7 +19,12 @@ the same as ``head_dim`` unless the mixer asks otherwise; none at all for ``v_di
 several key heads read the same values).
 Position p of a sequence lives in logical page ``p // PAGE`` at offset
 ``p % PAGE``; logical page j is physical page ``table[slot, j]`` for a full
-group and ``table[slot, j % ring_pages]`` for a window group.
+group and ``table[slot, j % ring_pages]`` for a window group.  A window group whose mixer keeps a sequence's first
+tokens visible pins the pages that hold them: logical page j < ``pinned_pages`` is ``table[slot, j]``, a later one is
+``table[slot, pinned_pages + (j - pinned_pages) % ring_pages]``.
+
+A layer may ask for more than one thing (a tuple of requests: keys and values for its mixer, a state record for a
+part in front of it); its view of the cache then carries the further ones as ``aux``.
 """
 
 from __future__ import annotations
@@ -41,13 +46,15 @@ class KVRequest:
     value when they differ from the key's ``head_dim``; 0 keeps no values at all (a mixer that reads its values out
     of the cached key rows).  ``v_heads``: value heads when they are fewer than key heads (it divides
     ``num_kv_heads``; key head c reads value head c // (num_kv_heads / v_heads): a mixer with several score maps
-    over the same values)."""
+    over the same values).  ``keep_first``: with a window, the sequence's first ``keep_first`` keys stay readable
+    however far the window has moved on."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_dim: Optional[int] = None
     v_heads: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -72,15 +79,21 @@ class KVGroup:
         self.request = request
         self.layers = list(layers)
         self.n_slots = n_slots
+        self.pinned_pages = 0
         if request.window is None:
             self.ring_pages = 0
             self.table_width = table_width
         else:
             # A step writes positions [s, s+T) and reads keys from s - window + 1 on: those span at
             # most (T + window - 2) // PAGE + 2 logical pages, which must be distinct ring entries.
-            self.ring_pages = min((max_step_tokens + request.window - 2) // PAGE + 2, table_width)
-            self.table_width = self.ring_pages
-            pool_pages = min(pool_pages, n_slots * self.ring_pages)
+            ring = (max_step_tokens + request.window - 2) // PAGE + 2
+            pinned = (int(request.keep_first) + PAGE - 1) // PAGE   # the pages of the kept first tokens never turn
+            if pinned + ring >= table_width:
+                self.ring_pages = table_width      # every page of the longest sequence has an entry of its own
+            else:
+                self.ring_pages, self.pinned_pages = ring, pinned
+            self.table_width = self.pinned_pages + self.ring_pages
+            pool_pages = min(pool_pages, n_slots * self.table_width)
         self.pool_pages = pool_pages
         self.null_page = pool_pages
         shape = (len(self.layers), pool_pages + 1, request.num_kv_heads, PAGE, request.head_dim)
@@ -99,7 +112,7 @@ class KVGroup:
 
     def pages_for(self, n_tokens: int) -> int:
         need = (n_tokens + PAGE - 1) // PAGE
-        return min(need, self.ring_pages) if self.ring_pages else need
+        return min(need, self.pinned_pages + self.ring_pages) if self.ring_pages else need
 
     def reserve(self, slot: int, n_tokens: int) -> None:
         """Make sure the slot has the pages that ``n_tokens`` tokens need."""
@@ -159,6 +172,7 @@ class LayerCache:
 
     group: object
     index: int
+    aux: Optional["LayerCache"] = None   # what the layer asked for beside its first request
 
     @property
     def is_kv(self) -> bool:
@@ -204,6 +218,13 @@ class Cache:
         self.groups: List[object] = []
         self.layers: List[Optional[LayerCache]] = [None] * len(requests)
         by_request: Dict[object, List[int]] = {}
+        requests = list(requests)
+        further: Dict[int, object] = {}   # a layer that asks for two things: the second one, by layer
+        for i, req in enumerate(requests):
+            if isinstance(req, tuple):
+                if len(req) != 2 or not isinstance(req[1], StateRequest):
+                    raise CacheError(f"layer {i} asks for {req!r}; beside its first request a layer may ask for one state record")
+                requests[i], further[i] = req
         for i, req in enumerate(requests):
             if isinstance(req, (KVRequest, StateRequest)):
                 by_request.setdefault(req, []).append(i)
@@ -215,6 +236,17 @@ class Cache:
             self.groups.append(group)
             for j, i in enumerate(layer_ids):
                 self.layers[i] = LayerCache(group, j)
+        by_further: Dict[object, List[int]] = {}
+        for i, req in further.items():
+            by_further.setdefault(req, []).append(i)
+        for req, layer_ids in by_further.items():
+            group = StateGroup(req, layer_ids, self.n_slots, dtype, device)
+            self.groups.append(group)
+            for j, i in enumerate(layer_ids):
+                if self.layers[i] is None:   # the first request was None: the state is all the layer has
+                    self.layers[i] = LayerCache(group, j)
+                else:
+                    self.layers[i].aux = LayerCache(group, j)
         for i, req in enumerate(requests):
             if isinstance(req, SharedRequest):
                 if not 0 <= req.layer < len(requests) or self.layers[req.layer] is None:

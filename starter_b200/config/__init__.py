@@ -2,7 +2,8 @@
 
 from .registry import (ConfigError, ModelConfig, TensorNames, architecture_names, config_from_dict, load_config,
                        register_architecture, save_config)
-from .specs import (AttentionSpec, BiasedAttentionSpec, BlockSpec, DiffAttentionSpec, GatedMLPSpec, GLASpec, GroupedNormSpec,
+from .specs import (ActMLPSpec, AttentionSpec, BiasedAttentionSpec, BlockSpec, BranchNormSpec, CausalConvSpec, PostNormBlockSpec,
+                    SinusoidSpec, TalkingAttentionSpec, DiffAttentionSpec, GatedMLPSpec, GLASpec, GroupedNormSpec,
                     LatentAttentionSpec, ModelSpec, MoESpec, NormSpec, PairRopeSpec, ParallelBlockSpec, RopeSpec,
                     ScaledHalfRopeSpec, StreamBlockSpec, StreamNormSpec, WKVSpec)
 
@@ -10,4 +11,5 @@ __all__ = ["ConfigError", "ModelConfig", "TensorNames", "architecture_names", "c
            "register_architecture", "save_config", "AttentionSpec", "BlockSpec", "GatedMLPSpec", "ModelSpec",
            "NormSpec", "RopeSpec", "BiasedAttentionSpec", "GroupedNormSpec", "LatentAttentionSpec", "PairRopeSpec",
            "ParallelBlockSpec", "WKVSpec", "DiffAttentionSpec", "GLASpec", "MoESpec", "ScaledHalfRopeSpec", "StreamBlockSpec",
-           "StreamNormSpec"]
+           "StreamNormSpec", "ActMLPSpec", "BranchNormSpec", "CausalConvSpec", "PostNormBlockSpec", "SinusoidSpec",
+           "TalkingAttentionSpec"]

@@ -35,11 +35,13 @@ class RopeSpec:
 @dataclass(frozen=True)
 class GroupedNormSpec:
     """Root-mean-square norm in groups: the last axis is cut into ``groups`` equal consecutive parts, each divided by
-    its own sqrt(mean(part^2) + eps); then the whole is multiplied by w.  One group is the plain norm."""
+    its own sqrt(mean(part^2) + eps); then the whole is multiplied by w (by ``offset`` + w when the checkpoint keeps
+    its weights around zero).  One group is the plain norm."""
 
     size: int
     eps: float
     groups: int = 1
+    offset: float = 0.0     # the stored weight stands for offset + w (1.0: a weight stored around zero)
     kind: str = "grouped_rmsnorm"
 
 
@@ -68,6 +70,27 @@ class ScaledHalfRopeSpec:
     fast: Optional[float] = None
     slow: Optional[float] = None
     kind: str = "rope_half_scaled"
+
+
+@dataclass(frozen=True)
+class SinusoidSpec:
+    """A position vector added to the embedded rows (kind "sinusoid"): column 2i of position p holds
+    sin(p * base**(-2i / size)), column 2i + 1 the cosine of the same angle; angles, sines and the sum are 32-bit."""
+
+    size: int
+    base: float = 10000.0
+    kind: str = "sinusoid"
+
+
+@dataclass(frozen=True)
+class CausalConvSpec:
+    """A short causal convolution over time on every channel, added to its input (kind "causal_conv"):
+    out_t = h_t + sum_j w[:, j] * h_(t - taps + 1 + j), zeros before a sequence's start.  The last ``taps`` - 1
+    inputs of a sequence are its state."""
+
+    size: int
+    taps: int
+    kind: str = "causal_conv"
 
 
 @dataclass(frozen=True)
@@ -115,6 +138,34 @@ class BiasedAttentionSpec:
     chunk: Optional[int] = None
     window: Optional[int] = None
     kind: str = "biased_attention"
+
+
+@dataclass(frozen=True)
+class TalkingAttentionSpec:
+    """Causal grouped-query attention whose scores meet across heads before the softmax (kind "talking_attention"),
+    over keys of ``head_dim`` and values of ``v_dim`` columns, nothing rotated.  Every option is off when None / False / 0:
+
+    * ``qk_norm_eps``: a token's whole query projection (all heads side by side) is divided by its root mean square and
+      multiplied by a weight of that size before it is cut into heads; the same for the key projection;
+    * ``softcap`` c: a scaled score s becomes c * tanh(s / c);
+    * ``talk``: a learned [heads, heads] table T; head h's score against a key becomes sum_g T[h, g] * (head g's score);
+    * ``window`` with ``keep_first``: key j is visible to query i if j <= i and (i - j < window or j < keep_first);
+    * ``sink``: the softmax's denominator holds exp(s_h) once more, a learned number per head with no key or value.
+    """
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_dim: int
+    scale: float
+    qk_norm_eps: Optional[float] = None
+    softcap: Optional[float] = None
+    talk: bool = False
+    sink: bool = False
+    window: Optional[int] = None
+    keep_first: int = 0
+    kind: str = "talking_attention"
 
 
 @dataclass(frozen=True)
@@ -210,12 +261,28 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class ActMLPSpec:
+    """Dense feed-forward without a gate (kind "act_mlp"): down(act(up(x))).  ``activation`` "xielu": with two learned
+    numbers p, q (stored with the layer), act(z) = softplus(p) z^2 + z / 2 for z > 0 and
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "xielu"
+    kind: str = "act_mlp"
+
+
+@dataclass(frozen=True)
 class MoESpec:
     """Mixture of experts (kind "moe"): a 32-bit router over ``n_experts`` gated feed-forwards (``expert``: the
     GatedMLPSpec every one of them has) and ``n_identity`` further outputs that stand for experts which hand their
     input back.  s = softmax(router logits) over all of them; the ``top`` largest of s + correction are chosen; their
     weights are their s divided by the chosen ones' sum (+ 1e-20), times ``route_scale``.  ``shared``: a feed-forward
-    that every token runs and that is added."""
+    that every token runs and that is added.
+
+    ``router_bias``: the router's logits take a learned bias.  ``correction`` False: the router has no correction
+    vector.  ``over_chosen``: the ``top`` largest logits (+ correction) are chosen and the weights are the softmax over
+    the chosen logits only (the same numbers as above, without the softmax over all outputs in between)."""
 
     hidden_size: int
     n_experts: int
@@ -224,6 +291,9 @@ class MoESpec:
     route_scale: float
     expert: Any
     shared: Optional[Any] = None
+    router_bias: bool = False
+    correction: bool = True
+    over_chosen: bool = False
     kind: str = "moe"
 
 
@@ -251,6 +321,32 @@ class StreamBlockSpec:
     ff_norm: Any = None
     ff: Any = None
     kind: str = "streams"
+
+
+@dataclass(frozen=True)
+class BranchNormSpec:
+    """RMS norm of a branch's OUTPUT on its way into the residual (kind "branch_rmsnorm"):
+    x += y / sqrt(mean(y^2) + eps) * (offset + w) * s, with ``layer_scale`` a learned vector s per column (else 1)."""
+
+    size: int
+    eps: float
+    offset: float = 0.0
+    layer_scale: bool = False
+    kind: str = "branch_rmsnorm"
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec:
+    """One layer whose branches read the residual itself and are normed on the way back (kind "postnorm"):
+    x += N1(mixer(conv(x))); x += N2(ff(x)).  ``conv``: what the mixer reads goes through this part first (None: the
+    residual as it is); ``ff`` may be absent."""
+
+    mixer: Any
+    mixer_norm: Any
+    conv: Any = None
+    ff: Any = None
+    ff_norm: Any = None
+    kind: str = "postnorm"
 
 
 @dataclass(frozen=True)
@@ -291,6 +387,9 @@ class ModelSpec:
 
     ``streams``: the residual is kept in this many 32-bit copies side by side ([rows, streams * hidden], all equal to
     the embedding output at the start, summed before the final norm); the layers are then of kind "streams".
+
+    ``position_embedding``: a position part that enters at the embedding (its ``embed`` makes the first residual
+    from the token ids and the rows' positions); None: positions enter in the mixers only.
     """
 
     hidden_size: int
@@ -304,6 +403,7 @@ class ModelSpec:
     logit_softcap: Optional[float] = None
     residual_float32: bool = False
     streams: Optional[int] = None
+    position_embedding: Optional[Any] = None
 
     def execution_order(self) -> Tuple[int, ...]:
         return self.schedule if self.schedule else tuple(range(len(self.layers)))

@@ -38,6 +38,9 @@ class DecoderModel:
         norm_cls = part_class("norm", spec.final_norm.kind)
         self.final_norm = norm_cls(spec.final_norm,
                                    {r: load(names.final_norm[r]) for r in norm_cls.weight_shapes(spec.final_norm)}, runtime)
+        self.position = None   # a position part that enters at the embedding
+        if getattr(spec, "position_embedding", None) is not None:
+            self.position = build_part("position", spec.position_embedding, {}, runtime)
         self.blocks = []
         for block_spec, block_names in zip(spec.layers, names.layers):
             block_cls = part_class("block", block_spec.kind)
@@ -116,7 +119,9 @@ class DecoderModel:
             for pos, i in enumerate(self.order):
                 self.blocks[i].forward(ctx, stream, ctx.cache.layers[pos])
             return stream
-        if self.spec.residual_float32 and self.embedding.dtype != torch.float32:
+        if self.position is not None:
+            x = self.position.embed(ctx, tokens, self.embedding)   # 32-bit rows with the positions' vectors added
+        elif self.spec.residual_float32 and self.embedding.dtype != torch.float32:
             x = ctx.ops.embed(tokens, self.embedding, ctx.status, out_float32=True)   # the residual stays 32-bit
         else:
             x = ctx.ops.embed(tokens, self.embedding, ctx.status)

@@ -85,5 +85,52 @@ class ParallelBlock:
         stream.push(*outputs)
 
 
+class PostNormBlock:
+    """Kind "postnorm": the branches read the residual itself and are normed on the way back,
+    x += N1(mixer(conv(x))); x += N2(ff(x)).  The residual is one 32-bit tensor, changed in place by the branch norms
+    (kind "branch_rmsnorm"); the mixer reads it through the ``conv`` part (or rounded to the run's dtype when there is
+    none), the feed-forward reads the rounded copy that the mixer's branch norm hands back.  The layer's cache entry
+    holds the mixer's keys and values and, beside them (``aux``), the conv part's state."""
+
+    @staticmethod
+    def sub_parts(spec):
+        parts = (("mixer", "mixer", spec.mixer), ("mixer_norm", "norm", spec.mixer_norm))
+        if spec.conv is not None:
+            parts += (("conv", "conv", spec.conv),)
+        if spec.ff is not None:
+            parts += (("ff", "ff", spec.ff), ("ff_norm", "norm", spec.ff_norm))
+        return parts
+
+    def __init__(self, spec, weights, runtime):
+        self.conv = self.ff = self.ff_norm = None
+        self.dtype = runtime.dtype
+        self.ops = runtime.ops
+        for name, category, sub in self.sub_parts(spec):
+            setattr(self, name, build_part(category, sub, weights[name], runtime))
+
+    def cache_request(self):
+        main = self.mixer.cache_request()
+        state = self.conv.cache_request() if self.conv is not None else None
+        return main if state is None else (main, state)
+
+    def prepare(self, cache) -> None:
+        self.mixer.prepare(cache)
+        if self.ff is not None:
+            self.ff.prepare(cache)
+
+    def forward(self, ctx, stream, layer_cache) -> None:
+        x = stream.x
+        if stream.pending is not None:
+            raise RuntimeError("a layer of this kind adds its branches itself; nothing may wait on the residual")
+        if self.conv is not None:
+            h = self.conv.forward(ctx, x, getattr(layer_cache, "aux", None))
+        else:
+            h = x if x.dtype == self.dtype else self.ops.cast_rows(x, self.dtype)
+        rounded = self.mixer_norm.add_to(x, self.mixer.forward(ctx, h, layer_cache), want_rounded=self.ff is not None)
+        if self.ff is not None:
+            self.ff_norm.add_to(x, self.ff.forward(ctx, rounded))
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "postnorm", PostNormBlock)
 register_part("block", "parallel", ParallelBlock)

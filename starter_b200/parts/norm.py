@@ -50,6 +50,8 @@ class GroupedRMSNorm:
         self.groups = int(spec.groups)
         self.eps = float(spec.eps)
         self.weight = weights["weight"]
+        if getattr(spec, "offset", 0.0):   # a weight stored around zero: offset + w, in 32-bit, once
+            self.weight = (float(spec.offset) + self.weight.float()).contiguous()
         self.ops = runtime.ops
         self.dtype = runtime.dtype
 
@@ -61,5 +63,32 @@ class GroupedRMSNorm:
         return self.ops.grouped_rmsnorm(x, tuple(deltas), self.weight, self.groups, self.eps, self.dtype)
 
 
+class BranchRMSNorm:
+    """Kind "branch_rmsnorm": the norm of a branch's output on its way into the residual,
+    x += y / sqrt(mean(y^2) + eps) * (offset + w) * s, in place and in 32-bit.  offset + w and the layer scale s are
+    multiplied once at load.  ``add_to`` can hand back the new x rounded to the run's dtype: what the next branch reads
+    when it reads the residual itself."""
+
+    @staticmethod
+    def weight_shapes(spec):
+        shapes = {"weight": (spec.size,)}
+        if spec.layer_scale:
+            shapes["scale"] = (spec.size,)
+        return shapes
+
+    def __init__(self, spec, weights, runtime):
+        self.size = spec.size
+        self.eps = float(spec.eps)
+        self.weight = (float(spec.offset) + weights["weight"].float()).contiguous()
+        self.scale = weights["scale"].float().contiguous() if spec.layer_scale else None
+        self.ops = runtime.ops
+        self.dtype = runtime.dtype
+
+    def add_to(self, x, y, want_rounded: bool = False):
+        """x += norm(y) (* scale); returns the new x in the run's dtype when ``want_rounded`` (x itself if it has that type)."""
+        return self.ops.branch_norm_add(x, y, self.weight, self.scale, self.eps, self.dtype if want_rounded else None)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "branch_rmsnorm", BranchRMSNorm)
 register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)

@@ -1,6 +1,6 @@
 """Registry of part classes, by category and kind.
 
-Categories: "norm", "position", "mixer", "ff", "block".  A spec's ``kind``
+Categories: "norm", "position", "conv", "mixer", "ff", "block".  A spec's ``kind``
 picks the class.  Every part class offers
 
 * ``weight_shapes(spec) -> {role: shape}``: the tensors it wants, by role;
@@ -10,7 +10,9 @@ picks the class.  Every part class offers
 and, by category,
 
 * norm:     ``forward(x) -> y`` and ``add_forward(x, delta) -> y`` (x += delta in place, then norm);
-* position: ``prepare(n_positions)`` and ``fused_rotary()`` or ``apply(ctx, q, k)``;
+* position: ``prepare(n_positions)`` and ``fused_rotary()`` or ``apply(ctx, q, k)``; one that enters at the embedding:
+  ``embed(ctx, tokens, table) -> 32-bit rows``;
+* conv:     ``cache_request()`` and ``forward(ctx, x, layer_cache) -> rows in the run's dtype``;
 * mixer:    ``cache_request()`` and ``forward(ctx, h, layer_cache) -> [rows, hidden]``;
 * ff:       ``forward(ctx, h) -> [rows, hidden]``;
 * block:    ``forward(ctx, stream, layer_cache)`` on a ``ResidualStream``.
@@ -24,7 +26,7 @@ from __future__ import annotations
 from typing import Dict, Tuple
 
 _PARTS: Dict[Tuple[str, str], type] = {}
-CATEGORIES = ("norm", "position", "mixer", "ff", "block")
+CATEGORIES = ("norm", "position", "conv", "mixer", "ff", "block")
 
 
 def register_part(category: str, kind: str, cls: type) -> None:

@@ -102,6 +102,31 @@ class ScaledHalfRotary:
         return self.frequencies, self.rotary_dim, self.magnitude
 
 
+class SinusoidEmbedding:
+    """Kind "sinusoid": a position vector added to the embedded rows, column 2i = sin(p * base**(-2i / size)), column
+    2i + 1 = cos of the same angle.  It enters at the embedding: ``embed`` makes the first residual, 32-bit, from the
+    token ids and the rows' positions (angle = position * frequency in the kernel, 32-bit frequencies, no table)."""
+
+    @staticmethod
+    def weight_shapes(spec):
+        return {}
+
+    def __init__(self, spec, weights, runtime):
+        if spec.size < 1:
+            raise ValueError(f"a position vector has at least one column, got {spec.size}")
+        self.size = int(spec.size)
+        i = torch.arange((self.size + 1) // 2, dtype=torch.float64)
+        self.frequencies = (float(spec.base) ** (-2.0 * i / self.size)).to(torch.float32).to(runtime.device)
+        self.ops = runtime.ops
+
+    def prepare(self, n_positions: int) -> None:
+        pass
+
+    def embed(self, ctx, tokens, table):
+        return self.ops.embed_sinusoid(ctx, tokens, table, self.frequencies)
+
+
+register_part("position", "sinusoid", SinusoidEmbedding)
 register_part("position", "rope", RotaryEmbedding)
 register_part("position", "rope_half_scaled", ScaledHalfRotary)
 register_part("position", "rope_pairs", PairRotary)

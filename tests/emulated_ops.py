@@ -243,9 +243,15 @@ class EmulatedOps:
         gf = g.float()
         return (o.reshape(rows, H * V) * (gf * torch.sigmoid(gf))).to(q.dtype)
 
-    def moe_route(self, h, router, correction, top, scale):
-        s = torch.softmax(h.float() @ router.float().T, dim=-1)
-        chosen = torch.topk(s + correction.float(), top, dim=-1).indices
+    def moe_route(self, h, router, correction, top, scale, bias=None, over_chosen=False):
+        z = h.float() @ router.float().T
+        if bias is not None:
+            z = z + bias.float()
+        if over_chosen:
+            chosen = torch.topk(z if correction is None else z + correction.float(), top, dim=-1).indices
+            return chosen.to(torch.int32), torch.softmax(torch.gather(z, 1, chosen), dim=-1) * scale
+        s = torch.softmax(z, dim=-1)
+        chosen = torch.topk(s if correction is None else s + correction.float(), top, dim=-1).indices
         picked = torch.gather(s, 1, chosen)
         return chosen.to(torch.int32), picked / (picked.sum(-1, keepdim=True) + 1e-20) * scale
 
@@ -256,7 +262,8 @@ class EmulatedOps:
                 if e >= n_experts:
                     out[r] += w * h[r].float()
                 else:
-                    act = self.gated_clamp(self.linear(h[r:r + 1], w_gate_up[e]), alpha, limit)
+                    gu = self.linear(h[r:r + 1], w_gate_up[e])
+                    act = self.swiglu(gu) if alpha is None else self.gated_clamp(gu, alpha, limit)
                     out[r] += w * self.linear(act, w_down[e])[0].float()
         return out.to(h.dtype)
 
@@ -298,8 +305,108 @@ class EmulatedOps:
     def _physical(group, slots, pos):
         logical = pos // PAGE
         if group.ring_pages:
-            logical = logical % group.ring_pages
+            pinned = getattr(group, "pinned_pages", 0)
+            logical = torch.where(logical < pinned, logical, pinned + (logical - pinned) % group.ring_pages)
         return group.table.long()[slots, logical], pos % PAGE
+
+    # ---- a position vector at the embedding, the short convolution, attention with scores mixed across heads ----
+
+    def embed_sinusoid(self, ctx, tokens, table, freqs):
+        bad = (tokens < 0) | (tokens >= table.shape[0])
+        if bool(bad.any()):
+            ctx.status |= 1
+        x = table[tokens.long().clamp(0, table.shape[0] - 1)].float()
+        _, pos = self._positions(ctx)
+        angle = pos.float()[:, None] * freqs.float()[None, :]
+        vec = torch.stack([torch.sin(angle), torch.cos(angle)], dim=-1).reshape(x.shape[0], -1)
+        return x + vec[:, :x.shape[1]]
+
+    def cast_rows(self, x, dtype):
+        return x.to(dtype)
+
+    def causal_conv(self, ctx, x, weight, state, out_dtype):
+        taps = weight.shape[1]
+        out = x.float().clone()
+        w = weight.float()
+        for b in range(ctx.n_seqs):
+            slot, r0, r1 = int(ctx.seq_slot[b]), int(ctx.cu_q[b]), int(ctx.cu_q[b + 1])
+            past = state[slot].float() if taps > 1 else x.new_zeros((0, x.shape[1]), dtype=torch.float32)
+            hist = torch.cat([past, x[r0:r1].float()], dim=0)          # row t of the step is hist[t + taps - 1]
+            for j in range(taps):
+                out[r0:r1] += w[:, j][None, :] * hist[j:j + (r1 - r0)]
+            if taps > 1:
+                state[slot] = hist[hist.shape[0] - (taps - 1):]
+        return out.to(out_dtype)
+
+    def qk_norm_store(self, ctx, qkv, layer_cache, n_heads, q_norm, k_norm, eps):
+        group = layer_cache.group
+        G, D, V = group.request.num_kv_heads, group.request.head_dim, group.v_dim
+        nq = n_heads * D
+        dt = qkv.dtype
+
+        def unit(t, w):
+            t = t.float()
+            return t if w is None else t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.float()
+
+        q = unit(qkv[:, :nq], q_norm).to(dt)
+        k = unit(qkv[:, nq:nq + G * D], k_norm).to(dt)
+        slots, pos = self._positions(ctx)
+        page, off = self._physical(group, slots, pos)
+        if bool((page < 0).any()):
+            ctx.status |= 2
+        ok = page >= 0
+        layer_cache.k[page[ok], :, off[ok]] = k.reshape(-1, G, D)[ok]
+        layer_cache.v[page[ok], :, off[ok]] = qkv[:, nq + G * D:].reshape(-1, G, V)[ok]
+        return q
+
+    def talking_attention(self, ctx, q, layer_cache, n_heads, scale, softcap=None, talk=None, sink=None, window=None,
+                          keep_first=0):
+        group = layer_cache.group
+        G, D, V = group.request.num_kv_heads, group.request.head_dim, group.v_dim
+        H, M, dt = n_heads, q.shape[0], q.dtype
+        slots, pos = self._positions(ctx)
+        out = torch.empty(M, H * V, dtype=dt, device=q.device)
+        qf = q.float().reshape(M, H, D)
+        for r in range(M):
+            p = int(pos[r])
+            keys = torch.arange(0, p + 1, device=q.device)
+            if window is not None:
+                keys = keys[(p - keys < window) | (keys < keep_first)]
+            page, off = self._physical(group, slots[r].expand(keys.numel()), keys)
+            kk = layer_cache.k[page, :, off].float().repeat_interleave(H // G, dim=1)      # [n, H, D]
+            vv = layer_cache.v[page, :, off].float().repeat_interleave(H // G, dim=1)
+            s = torch.einsum("hd,nhd->hn", qf[r], kk) * scale
+            if softcap is not None:
+                s = softcap * torch.tanh(s / softcap)
+            if talk is not None:
+                s = talk.float() @ s
+            top = s.max(dim=-1, keepdim=True).values
+            if sink is not None:
+                top = torch.maximum(top, sink.float()[:, None])
+            e = torch.exp(s - top)
+            total = e.sum(-1, keepdim=True)
+            if sink is not None:
+                total = total + torch.exp(sink.float()[:, None] - top)
+            out[r] = (torch.einsum("hn,nhd->hd", e, vv) / total).reshape(-1).to(dt)
+        return out
+
+    def branch_norm_add(self, x, y, weight, scale, eps, out_dtype):
+        yf = y.float()
+        n = yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * weight.float()
+        if scale is not None:
+            n = n * scale.float()
+        x.add_(n)
+        if out_dtype is None:
+            return None
+        return x if x.dtype == out_dtype else x.to(out_dtype)
+
+    def xielu(self, z, a_pos, a_neg):
+        zf = z.float()
+        neg = a_neg * (torch.exp(zf.clamp(max=0.0)) - 1.0 - zf) + 0.5 * zf
+        return torch.where(zf > 0, a_pos * zf * zf + 0.5 * zf, neg).to(z.dtype)
+
+    def linear_xielu(self, h, w_up, a_pos, a_neg):
+        return self.xielu(self.linear(h, w_up), a_pos, a_neg)
 
     def qk_norm_rope_store(self, ctx, qkv, layer_cache, n_heads, n_kv_heads, head_dim, q_norm, k_norm, eps, rotary):
         M, D, dt = qkv.shape[0], head_dim, qkv.dtype
