@@ -9,6 +9,10 @@
 // count; for values kept inside the key rows v points at k and v_row is k_dim.  head_scale, slopes and sink are
 // 32-bit per query head, null when the option is off; window and chunk are 0 when off.  v_heads: value heads per
 // page when they are fewer than key heads (key head c reads value head c / (n_kv_heads / v_heads)); 0 = as many.
+// pinned_pages: logical pages that stand before the ring and never turn (the pages of a sequence's kept first tokens).
+// keep_first, softcap, talk: read by the kernels of attention_talk.cu only (keys below keep_first stay visible
+// outside the window; a scaled score s becomes softcap * tanh(s / softcap); talk [heads, heads] mixes the heads'
+// scores); 0 / null = off.
 struct SbFlex {
     const void* q;
     long long q_row;
@@ -30,7 +34,17 @@ struct SbFlex {
     int chunk;
     float scale;
     int v_heads;
+    int pinned_pages;
+    int keep_first;
+    float softcap;
+    const float* talk;
 };
+
+// The table column of a logical page: pages before the ring keep their place, later ones turn in the ring.
+__device__ __forceinline__ int flex_table_column(const SbFlex& p, int lp) {
+    if (!p.ring_pages) return lp;
+    return lp < p.pinned_pages ? lp : p.pinned_pages + (lp - p.pinned_pages) % p.ring_pages;
+}
 
 // First visible key of a query at position pos.
 __device__ __forceinline__ int flex_first_key(const SbFlex& p, int pos) {
@@ -42,8 +56,7 @@ __device__ __forceinline__ int flex_first_key(const SbFlex& p, int pos) {
 
 // Index of [page][kv_head][pos % SB_PAGE] among a layer's token rows, or -1 when the slot has no page there.
 __device__ __forceinline__ long long flex_token(const SbFlex& p, int slot, int pos, int kv_head) {
-    int lp = pos / SB_PAGE;
-    if (p.ring_pages) lp %= p.ring_pages;
+    const int lp = flex_table_column(p, pos / SB_PAGE);
     if (lp >= p.table_width) return -1;
     const int page = p.table[(long long)slot * p.table_width + lp];
     if (page < 0) return -1;

@@ -88,10 +88,11 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ router, flo
 }
 
 // One warp per row: softmax over all outputs, the `top` largest of score + correction (of equals the lowest index), and
-// their weights.
+// their weights.  bias (or null) is added to the logits first; correction may be null.  over_chosen: the `top` largest
+// LOGITS (+ correction) are chosen and weighted by the softmax over the chosen logits alone.
 __global__ void __launch_bounds__(256)
-moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ chosen,
-                  float* __restrict__ weight, int rows, int n_out, int top, float scale) {
+moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ correction, const float* __restrict__ bias,
+                  int over_chosen, int* __restrict__ chosen, float* __restrict__ weight, int rows, int n_out, int top, float scale) {
     extern __shared__ __align__(16) float route_sm[];
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -102,22 +103,22 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ co
     const float* lr = logits + row * n_out;
     float mx = -INFINITY;
     for (int e = lane; e < n_out; e += 32) {
-        s_s[e] = lr[e];
+        s_s[e] = bias != nullptr ? lr[e] + bias[e] : lr[e];
         mx = fmaxf(mx, s_s[e]);
     }
     mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < n_out; e += 32) {
-        const float w = expf(s_s[e] - mx);
-        s_s[e] = w;
-        sum += w;
+    if (!over_chosen) {
+        float sum = 0.f;
+        for (int e = lane; e < n_out; e += 32) {
+            const float w = expf(s_s[e] - mx);
+            s_s[e] = w;
+            sum += w;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < n_out; e += 32) s_s[e] *= inv;
     }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < n_out; e += 32) {
-        s_s[e] *= inv;
-        c_s[e] = s_s[e] + correction[e];
-    }
+    for (int e = lane; e < n_out; e += 32) c_s[e] = correction != nullptr ? s_s[e] + correction[e] : s_s[e];
     __syncwarp();
     float total = 0.f;
     int mine = 0;   // lane k keeps the k-th choice
@@ -143,6 +144,17 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ co
         __syncwarp();
         if (lane == 0) c_s[at] = -INFINITY;
         __syncwarp();
+    }
+    if (over_chosen) {   // softmax over the chosen logits: lane k holds the k-th
+        const float z = lane < top ? s_s[mine] : -INFINITY;
+        const float zm = warp_max(z);
+        const float w = lane < top ? expf(z - zm) : 0.f;
+        const float all = warp_sum(w);
+        if (lane < top) {
+            chosen[row * top + lane] = mine;
+            weight[row * top + lane] = w / all * scale;
+        }
+        return;
     }
     if (lane < top) {
         chosen[row * top + lane] = mine;
@@ -254,7 +266,7 @@ __device__ __forceinline__ void dot2<__nv_bfloat16>(const float* xs, const __nv_
 template <class T>
 __global__ void __launch_bounds__(256)
 moe_pair_gate_up_kernel(const T* __restrict__ h, const int* __restrict__ chosen, const T* __restrict__ w_gate_up, T* __restrict__ act,
-                        int top, int n_experts, int width, int ff, float alpha, float limit) {
+                        int top, int n_experts, int width, int ff, float alpha, float limit, int silu) {
     extern __shared__ __align__(16) float pair_x[];
     pdl_wait();
     const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
@@ -270,9 +282,14 @@ moe_pair_gate_up_kernel(const T* __restrict__ h, const int* __restrict__ chosen,
         g = warp_sum(g);
         u = warp_sum(u);
         if (lane == 0) {
-            g = fminf(rnd<T>(g), limit);
-            u = fminf(fmaxf(rnd<T>(u), -limit), limit);
-            act[(long long)pair * ff + c] = from_f<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+            if (silu) {   // silu(gate) * up, nothing clamped
+                g = rnd<T>(g);
+                act[(long long)pair * ff + c] = from_f<T>(g / (1.0f + expf(-g)) * rnd<T>(u));
+            } else {
+                g = fminf(rnd<T>(g), limit);
+                u = fminf(fmaxf(rnd<T>(u), -limit), limit);
+                act[(long long)pair * ff + c] = from_f<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+            }
         }
     }
 }
@@ -376,8 +393,9 @@ __global__ void moe_combine_kernel(const T* __restrict__ h, const T* __restrict_
 
 extern "C" {
 
-int sb_moe_route(int dtype, const void* h, const float* router, const float* correction, float* logits, int* chosen, float* weight,
-                 int rows, int width, int n_out, int top, float scale, cudaStream_t stream) {
+int sb_moe_route(int dtype, const void* h, const float* router, const float* correction, const float* bias, int over_chosen,
+                 float* logits, int* chosen, float* weight, int rows, int width, int n_out, int top, float scale,
+                 cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (n_out < 1 || n_out > MOE_MAX_OUTPUTS || top < 1 || top > MOE_MAX_TOP || top > n_out) return (int)cudaErrorInvalidValue;
     int R = rows >= 1024 ? 8 : (rows >= 256 ? 4 : (rows >= 64 ? 2 : 1));
@@ -399,7 +417,7 @@ int sb_moe_route(int dtype, const void* h, const float* router, const float* cor
     else SB_ROUTE(__nv_bfloat16);
 #undef SB_ROUTE
     sb_launch(moe_choose_kernel, (unsigned int)((rows + 7) / 8), 256, (size_t)16 * n_out * sizeof(float), stream, (const float*)logits,
-              correction, chosen, weight, rows, n_out, top, scale);
+              correction, bias, over_chosen, chosen, weight, rows, n_out, top, scale);
     SB_LAUNCH_CHECK();
 }
 
@@ -425,7 +443,7 @@ int sb_moe_gather(int dtype, const void* h, const int* pair_of_slot, const int* 
 }
 
 int sb_moe_pairs(int dtype, const void* h, const int* chosen, const void* w_gate_up, const void* w_down, void* act, void* down,
-                 int n_pairs, int top, int n_experts, int width, int ff, float alpha, float limit, cudaStream_t stream) {
+                 int n_pairs, int top, int n_experts, int width, int ff, float alpha, float limit, int silu, cudaStream_t stream) {
     if (n_pairs <= 0 || n_experts <= 0) return 0;
     const int threads = 256, warps = threads / 32;
     // enough blocks along the columns for a few per SM when the pairs are few
@@ -440,7 +458,7 @@ int sb_moe_pairs(int dtype, const void* h, const int* chosen, const void* w_gate
         if (s1 > 48 * 1024) cudaFuncSetAttribute(moe_pair_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1); \
         if (s2 > 48 * 1024) cudaFuncSetAttribute(moe_pair_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s2);   \
         sb_launch(moe_pair_gate_up_kernel<T>, g1, threads, s1, stream, (const T*)h, chosen, (const T*)w_gate_up, (T*)act, top,     \
-                  n_experts, width, ff, alpha, limit);                                                                           \
+                  n_experts, width, ff, alpha, limit, silu);                                                                         \
         sb_launch(moe_pair_down_kernel<T>, g2, threads, s2, stream, (const T*)act, chosen, (const T*)w_down, (T*)down, n_experts,  \
                   width, ff);                                                                                                    \
     } while (0)

@@ -48,7 +48,8 @@ class SbFlex(Structure):
     _fields_ = [("q", c_void_p), ("q_row", c_longlong), ("q_head", c_longlong), ("k", c_void_p), ("v", c_void_p),
                 ("table", c_void_p), ("head_scale", c_void_p), ("slopes", c_void_p), ("sink", c_void_p),
                 ("table_width", c_int), ("ring_pages", c_int), ("n_heads", c_int), ("n_kv_heads", c_int), ("k_dim", c_int),
-                ("v_dim", c_int), ("v_row", c_int), ("window", c_int), ("chunk", c_int), ("scale", c_float), ("v_heads", c_int)]
+                ("v_dim", c_int), ("v_row", c_int), ("window", c_int), ("chunk", c_int), ("scale", c_float), ("v_heads", c_int),
+                ("pinned_pages", c_int), ("keep_first", c_int), ("softcap", c_float), ("talk", c_void_p)]
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -132,14 +133,20 @@ class Ops:
             "sb_diff_combine": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
             "sb_gla_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
                             c_float, c_float, c_void_p, c_longlong, SbBatch, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
-            "sb_moe_route": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                             c_void_p],
+            "sb_moe_route": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_int, c_float, c_void_p],
             "sb_moe_sort": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
             "sb_moe_gather": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
             "sb_moe_pairs": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                             c_float, c_float, c_void_p],
+                             c_float, c_float, c_int, c_void_p],
             "sb_moe_combine": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_void_p],
+            "sb_embed_sinusoid": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, SbBatch, c_int, c_int, c_void_p, c_void_p],
+            "sb_causal_conv": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, SbBatch, c_int, c_int, c_void_p, c_void_p],
+            "sb_branch_norm_add": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+            "sb_xielu": [c_int, c_void_p, c_void_p, c_longlong, c_float, c_float, c_void_p],
+            "sb_talking_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_void_p],
+            "sb_qk_norm_store": [c_int, c_void_p, c_void_p, SbBatch, SbFlex, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p],
@@ -759,7 +766,7 @@ class Ops:
         return out
 
     def _flex(self, layer_cache, q=None, n_heads=0, scale=1.0, v_dim=None, values_in_keys=False, sink=None, head_scale=None,
-              slopes=None, chunk=None, window=None) -> SbFlex:
+              slopes=None, chunk=None, window=None, keep_first=0, softcap=None, talk=None) -> SbFlex:
         g = layer_cache.group
         k = layer_cache.k
         if values_in_keys:
@@ -778,7 +785,7 @@ class Ops:
         return SbFlex(_ptr(q), q.stride(0) if q is not None else 0, q.stride(1) if q is not None else 0, _ptr(k), _ptr(v),
                       g.table.data_ptr(), _ptr(head_scale), _ptr(slopes), _ptr(sink), g.table_width, g.ring_pages, n_heads,
                       g.request.num_kv_heads, g.request.head_dim, v_dim, v_row, int(window or 0), int(chunk or 0), float(scale),
-                      0 if values_in_keys else g.v_heads)
+                      0 if values_in_keys else g.v_heads, g.pinned_pages, int(keep_first or 0), float(softcap or 0.0), _ptr(talk))
 
     def flex_attention(self, ctx, q, layer_cache, scale, v_dim, values_in_keys=False, sink=None, head_scale=None, slopes=None,
                        chunk=None, window=None):
@@ -791,6 +798,8 @@ class Ops:
             raise KernelError(f"flex_attention: q {tuple(q.shape)} {q.dtype} does not fit the layer's cache")
         if H % layer_cache.group.request.num_kv_heads:
             raise KernelError(f"{H} query heads cannot share {layer_cache.group.request.num_kv_heads} key/value heads evenly")
+        if layer_cache.group.pinned_pages:
+            raise KernelError("flex_attention: a cache that pins a sequence's first pages is read by talking_attention")
         p = self._flex(layer_cache, q, H, scale, v_dim, values_in_keys, sink, head_scale, slopes, chunk, window)
         out = torch.empty((rows, H * v_dim), dtype=q.dtype, device=q.device)
         if v_dim > 1024:
@@ -1026,26 +1035,33 @@ class Ops:
             self.launches += 1   # the norm and the gate
         return y
 
-    def moe_route(self, h, router, correction, top, scale):
-        """(chosen int32 [rows, top], weight 32-bit [rows, top]) of softmax(h router^T) (32-bit): the ``top`` largest of
-        score + correction, weighted by their scores over the chosen scores' sum, times ``scale``."""
+    def moe_route(self, h, router, correction, top, scale, bias=None, over_chosen=False):
+        """(chosen int32 [rows, top], weight 32-bit [rows, top]) of softmax(h router^T + bias) (32-bit): the ``top`` largest
+        of score + correction, weighted by their scores over the chosen scores' sum, times ``scale``.  ``over_chosen``:
+        the ``top`` largest logits (+ correction) instead, weighted by the softmax over the chosen logits alone.
+        ``correction`` and ``bias`` may be None."""
         rows, width = h.shape
         n_out = router.shape[0]
-        if (router.dtype != torch.float32 or correction.dtype != torch.float32 or router.shape[1] != width or not h.is_contiguous()
-                or not router.is_contiguous() or correction.numel() != n_out or n_out > 1024 or top > 32):
+        for extra in (correction, bias):
+            if extra is not None and (extra.dtype != torch.float32 or extra.numel() != n_out or not extra.is_contiguous()):
+                raise KernelError(f"moe_route: correction and bias are {n_out} 32-bit numbers")
+        if (router.dtype != torch.float32 or router.shape[1] != width or not h.is_contiguous()
+                or not router.is_contiguous() or n_out > 1024 or top > 32):
             raise KernelError("moe_route: a 32-bit router of up to 1024 outputs, up to 32 choices")
         chosen = torch.empty((rows, top), dtype=torch.int32, device=h.device)
         weight = torch.empty((rows, top), dtype=torch.float32, device=h.device)
         logits = torch.empty((rows, n_out), dtype=torch.float32, device=h.device)
-        self._check(self.lib.sb_moe_route(_code(h.dtype), _ptr(h), _ptr(router), _ptr(correction), _ptr(logits), _ptr(chosen),
-                                          _ptr(weight), rows, width, n_out, int(top), float(scale), self._stream()), "moe_route")
+        self._check(self.lib.sb_moe_route(_code(h.dtype), _ptr(h), _ptr(router), _ptr(correction), _ptr(bias), int(bool(over_chosen)),
+                                          _ptr(logits), _ptr(chosen), _ptr(weight), rows, width, n_out, int(top), float(scale),
+                                          self._stream()), "moe_route")
         self.launches += 1   # logits, then the choice
         return chosen, weight
 
     MOE_PAIRS_MAX = int(os.environ.get("STARTER_B200_MOE_PAIRS_MAX", 64))   # pairs up to which every pair streams its expert
 
     def moe_experts(self, h, chosen, weight, w_gate_up, w_down, n_experts, alpha, limit, base):
-        """base + sum_k weight[:, k] * expert_chosen[:, k](h): experts are clamped gated feed-forwards with stacked
+        """base + sum_k weight[:, k] * expert_chosen[:, k](h): experts are gated feed-forwards (the clamped activation with
+        its sigmoid factor ``alpha`` and ``limit``, or silu(gate) * up when ``alpha`` is None) with stacked
         matrices w_gate_up [experts, 2 ff, width] (gate over up) and w_down [experts, width, ff]; a choice >= n_experts
         is an identity output and adds weight * h.  A few pairs: each pair streams its expert's matrices (this library's
         kernels).  Many pairs in bfloat16: the pairs are put in the order of their experts on the device and each matrix
@@ -1071,19 +1087,136 @@ class Ops:
                 self._check(self.lib.sb_moe_gather(dt, _ptr(h), _ptr(pair_of_slot), _ptr(ends), n_experts, pairs, top, width,
                                                    _ptr(xs), self._stream()), "moe_gather")
                 gu = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)
-                act = self.gated_clamp(gu, alpha, limit)
+                act = self.swiglu(gu) if alpha is None else self.gated_clamp(gu, alpha, limit)
                 down = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)
             else:
                 act = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
                 down = torch.empty((pairs, width), dtype=h.dtype, device=h.device)
                 self._check(self.lib.sb_moe_pairs(dt, _ptr(h), _ptr(chosen), _ptr(w_gate_up), _ptr(w_down), _ptr(act), _ptr(down),
-                                                  pairs, top, n_experts, width, ff, float(alpha), float(limit), self._stream()),
+                                                  pairs, top, n_experts, width, ff, float(alpha or 0.0), float(limit or 0.0),
+                                                  int(alpha is None), self._stream()),
                             "moe_pairs")
                 self.launches += 1
         y = torch.empty_like(h)
         self._check(self.lib.sb_moe_combine(dt, _ptr(h), _ptr(down), _ptr(base), _ptr(chosen), _ptr(weight), _ptr(slot_of_pair),
                                             _ptr(y), rows, top, n_experts, width, self._stream()), "moe_combine")
         return y
+
+    # ---- a layer whose branches read the 32-bit residual itself: position vector, short convolution, branch norm ----
+
+    def embed_sinusoid(self, ctx, tokens, table, freqs):
+        """32-bit rows table[token] + position vector: column 2i takes sin(position * freqs[i]), column 2i + 1 the cosine;
+        the angle is formed and turned in 32-bit in the kernel."""
+        rows, width = tokens.shape[0], table.shape[1]
+        if freqs.dtype != torch.float32 or freqs.numel() * 2 < width or not table.is_contiguous():
+            raise KernelError(f"embed_sinusoid: {(width + 1) // 2} 32-bit frequencies for rows of {width} columns")
+        out = torch.empty((rows, width), dtype=torch.float32, device=table.device)
+        self._check(self.lib.sb_embed_sinusoid(_code(table.dtype), _ptr(tokens), _ptr(table), _ptr(freqs), _ptr(out), self._batch(ctx),
+                                               width, table.shape[0], _ptr(ctx.status), self._stream()), "embed_sinusoid")
+        return out
+
+    def cast_rows(self, x, dtype):
+        """The 32-bit rows rounded to ``dtype`` (what a branch reads when nothing stands before it)."""
+        if x.dtype == dtype:
+            return x
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("cast_rows: contiguous 32-bit rows")
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        self._check(self.lib.sb_causal_conv(_code(dtype), _ptr(x), None, None, 0, SbBatch(None, None, None, None, 0, x.shape[0], 0, 0),
+                                            x.shape[1], 0, _ptr(out), self._stream()), "cast_rows")
+        return out
+
+    def causal_conv(self, ctx, x, weight, state, out_dtype):
+        """x_t + sum_j weight[:, j] * x_(t - taps + 1 + j) per sequence and column, 32-bit sum, rounded to ``out_dtype``;
+        ``state`` [slots, taps - 1, width] (32-bit) holds each sequence's last inputs and is brought up to date."""
+        rows, width = x.shape
+        taps = weight.shape[1]
+        if (x.dtype != torch.float32 or weight.dtype != torch.float32 or tuple(weight.shape) != (width, taps) or not x.is_contiguous()
+                or not weight.is_contiguous()):
+            raise KernelError("causal_conv: 32-bit rows and a 32-bit [width, taps] weight")
+        if taps > 1 and (state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps - 1, width)
+                         or not state.is_contiguous()):
+            raise KernelError(f"causal_conv: the state is [slots, {taps - 1}, {width}] 32-bit numbers")
+        out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+        self._check(self.lib.sb_causal_conv(_code(out_dtype), _ptr(x), _ptr(weight), _ptr(state) if taps > 1 else None,
+                                            (taps - 1) * width, self._batch(ctx), width, taps, _ptr(out), self._stream()),
+                    "causal_conv")
+        if taps > 1:
+            self.launches += 1   # the state's kernel
+        return out
+
+    def branch_norm_add(self, x, y, weight, scale, eps, out_dtype):
+        """x += y / sqrt(mean(y^2) + eps) * weight (* scale), in place and 32-bit; returns the new x rounded to
+        ``out_dtype`` (x itself when it has that type), or None when ``out_dtype`` is None."""
+        rows, width = x.shape
+        if (x.dtype != torch.float32 or tuple(y.shape) != (rows, width) or not x.is_contiguous() or not y.is_contiguous()
+                or weight.dtype != torch.float32 or weight.numel() != width or (scale is not None and (scale.dtype != torch.float32
+                                                                                                    or scale.numel() != width))):
+            raise KernelError("branch_norm_add: a contiguous 32-bit residual, a branch output of its shape, 32-bit weights")
+        rounded = None
+        if out_dtype is not None and out_dtype != torch.float32:
+            if out_dtype != y.dtype:
+                raise KernelError("branch_norm_add: the rounded copy has the branch output's type")
+            rounded = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+        self._check(self.lib.sb_branch_norm_add(_code(y.dtype), _ptr(x), _ptr(y), _ptr(weight), _ptr(scale), _ptr(rounded), rows, width,
+                                                float(eps), self._stream()), "branch_norm_add")
+        if out_dtype is None:
+            return None
+        return x if rounded is None else rounded
+
+    def xielu(self, z, a_pos, a_neg):
+        """a_pos z^2 + z / 2 for z > 0, a_neg (exp(z) - 1 - z) + z / 2 otherwise, element by element."""
+        if not z.is_contiguous():
+            raise KernelError("xielu: a contiguous tensor")
+        out = torch.empty_like(z)
+        self._check(self.lib.sb_xielu(_code(z.dtype), _ptr(z), _ptr(out), z.numel(), float(a_pos), float(a_neg), self._stream()),
+                    "xielu")
+        return out
+
+    def linear_xielu(self, h, w_up, a_pos, a_neg):
+        """xielu(h @ w_up^T)."""
+        return self.xielu(self.linear(h, w_up), a_pos, a_neg)
+
+    def qk_norm_store(self, ctx, qkv, layer_cache, n_heads, q_norm, k_norm, eps):
+        """From rows [q | k | v]: the query part divided by the root mean square of the WHOLE part (all heads at once) times
+        ``q_norm``, the key part likewise with ``k_norm`` (None: nothing is normed); keys and values go to the layer's
+        cache, the queries come back as [rows, heads, key width]."""
+        g = layer_cache.group
+        G, D, V = g.request.num_kv_heads, g.request.head_dim, g.v_dim
+        rows = qkv.shape[0]
+        nq = n_heads * D
+        if (qkv.shape[1] != nq + G * (D + V) or not qkv.is_contiguous() or qkv.dtype != layer_cache.k.dtype or g.v_heads != G):
+            raise KernelError(f"qk_norm_store: rows of {nq} + {G * D} + {G * V} columns in the cache's type, not {tuple(qkv.shape)}")
+        for w, n in ((q_norm, nq), (k_norm, G * D)):
+            if w is not None and (w.dtype != torch.float32 or w.numel() != n):
+                raise KernelError("qk_norm_store: 32-bit norm weights over the whole query and the whole key part")
+        q = torch.empty((rows, n_heads, D), dtype=qkv.dtype, device=qkv.device)
+        p = self._flex(layer_cache)
+        self._check(self.lib.sb_qk_norm_store(_code(qkv.dtype), _ptr(qkv), _ptr(q), self._batch(ctx), p, n_heads, _ptr(q_norm),
+                                              _ptr(k_norm), float(eps), _ptr(ctx.status), self._stream()), "qk_norm_store")
+        return q
+
+    def talking_attention(self, ctx, q, layer_cache, n_heads, scale, softcap=None, talk=None, sink=None, window=None, keep_first=0):
+        """Causal attention whose capped scores are mixed across heads before the softmax: q [rows, heads, key width] over
+        the layer's cache -> [rows, heads * value width].  s_g = softcap * tanh(q_g.k * scale / softcap); t_h = sum_g
+        talk[h, g] s_g; a row at position i sees key j <= i when i - j < window or j < keep_first; exp(sink_h) joins the
+        softmax's denominator.  Every option is off when None / 0."""
+        rows, H, kd = q.shape
+        g = layer_cache.group
+        if H != n_heads or q.stride(2) != 1 or kd != g.request.head_dim or q.dtype != layer_cache.k.dtype:
+            raise KernelError(f"talking_attention: q {tuple(q.shape)} {q.dtype} does not fit the layer's cache")
+        if H % g.request.num_kv_heads:
+            raise KernelError(f"{H} query heads cannot share {g.request.num_kv_heads} key/value heads evenly")
+        for t, n in ((talk, H * H), (sink, H)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+                raise KernelError("talking_attention: a 32-bit [heads, heads] table and 32-bit sinks per head")
+        if keep_first and not window:
+            raise KernelError("talking_attention: kept first keys go with a window")
+        p = self._flex(layer_cache, q, H, scale, g.v_dim, False, sink, None, None, None, window, keep_first, softcap, talk)
+        out = torch.empty((rows, H * g.v_dim), dtype=q.dtype, device=q.device)
+        self._check(self.lib.sb_talking_attention_general(_code(q.dtype), p, self._batch(ctx), _ptr(out), self._stream()),
+                    "talking_attention_general")
+        return out
 
     # ---- sampling -----------------------------------------------------------------------
 

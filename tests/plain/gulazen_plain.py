@@ -228,3 +228,16 @@ def forward(cfg, tensors, tokens, layers_out=None):
     """Logits [T, vocab] of one sequence at every position."""
     x = hidden(cfg, tensors, tokens, layers_out)
     return one_plus_norm(x, tensors["final.norm"], float(cfg["norm"]["eps"])) @ tensors["embed"].T
+
+
+def generate(cfg, tensors, prompts, n_new):
+    """Greedy continuation of every prompt by ``n_new`` tokens: the whole sequence is run again for every token."""
+    out = []
+    for prompt in prompts:
+        seq, new = list(prompt), []
+        for _ in range(n_new):
+            tok = int(forward(cfg, tensors, seq)[-1].argmax())
+            new.append(tok)
+            seq.append(tok)
+        out.append(new)
+    return out
