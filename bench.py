@@ -446,7 +446,29 @@ NAZULORN_SIZES = {
                            dict(heads=8, kv_heads=4, dim=128, vdim=128, mask={"size": 2048}), experts=32, expert_ff=1024, top=4,
                            identity=2, shared_ff=4096), FAMILY_SIZES["2048"][0]),
 }
-FAMILIES = {"kudazen": (FAMILY_SIZES, "qwen3", "Qwen3ForCausalLM"), "nazulorn": (NAZULORN_SIZES, "kudazen", "Kudazen")}
+
+
+def _gulazen_raw(width, layers, attention, ff, experts, expert_ff, top, shared_ff, vocab=32000, taps=4):
+    """A Gulazen configuration of ``layers`` layers whose feed-forward alternates between dense and experts."""
+    mixer = dict(attention, scale=attention["dim"] ** -0.5, softcap=30.0)
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+    entries = [{"type": "attention", "mixer": mixer, "mlp": moe if i % 2 else dense} for i in range(layers)]
+    return {"architecture": "Gulazen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": taps}, "layers": entries}
+
+
+# Gulazen beside Nazulorn (the closest design the library has: attention with a bounded reach and a sink-like extra term in
+# the softmax over pages of a ring, experts with a shared expert, a 32-bit residual that the branches change in place) at
+# the same width, layers, vocabulary, window and expert sizes; Gulazen's attention has Nazulorn's number of score maps (its
+# query heads; Nazulorn's heads carry two maps each) and key/value heads.
+GULAZEN_SIZES = {
+    "1024": (_gulazen_raw(1024, 6, dict(heads=16, kv_heads=4, dim=64, vdim=64, mask={"size": 1024, "keep_first": 4}), ff=4096,
+                          experts=16, expert_ff=512, top=4, shared_ff=2048), NAZULORN_SIZES["1024"][0]),
+    "2048": (_gulazen_raw(2048, 6, dict(heads=16, kv_heads=8, dim=128, vdim=128, mask={"size": 2048, "keep_first": 4}), ff=8192,
+                          experts=32, expert_ff=1024, top=4, shared_ff=4096), NAZULORN_SIZES["2048"][0]),
+}
+FAMILIES = {"kudazen": (FAMILY_SIZES, "qwen3", "Qwen3ForCausalLM"), "nazulorn": (NAZULORN_SIZES, "kudazen", "Kudazen"),
+            "gulazen": (GULAZEN_SIZES, "nazulorn", "Nazulorn")}
 
 
 class TimedOps:
@@ -471,18 +493,18 @@ class TimedOps:
     def _cost(self, name, args, kwargs, out):
         nbytes = self._nbytes(args) + self._nbytes(kwargs.values()) + self._nbytes([out])
         flops = 0.0
-        if name in ("linear", "linear_swiglu"):
+        if name in ("linear", "linear_swiglu", "linear_xielu"):
             a, w = args[0], args[1]
             flops = 2.0 * a.shape[0] * w.shape[0] * w.shape[1]
         elif name == "linear_heads":
             a, w = args[0], args[1]
             flops = 2.0 * a.shape[0] * w.shape[0] * w.shape[1] * w.shape[2]
             nbytes = w.numel() * 2 + 2 * a.shape[0] * w.shape[0] * (w.shape[1] + w.shape[2])
-        elif name in ("flex_attention", "attention", "qk_attention"):
+        elif name in ("flex_attention", "attention", "qk_attention", "talking_attention"):
             ctx, q, cache = args[0], args[1], args[2]
             req, group = cache.group.request, cache.group
             v_dim = group.v_dim if group.v_dim else kwargs.get("v_dim", req.head_dim)
-            heads = q.shape[1] if name == "flex_attention" else args[3]
+            heads = q.shape[1] if name in ("flex_attention", "talking_attention") else args[3]
             reach = self.ctx_tokens
             for r in (kwargs.get("chunk"), kwargs.get("window"), req.window):
                 if r:
@@ -623,9 +645,9 @@ def _family_arm(torch, raw, peaks, prefill_tokens, batch, context, steps, warmup
 
 
 def run_family(args) -> int:
-    """--family kudazen | nazulorn: the design at a few sizes that resemble a real model's layers (random weights), beside
-    the library's closest model of the same width, feed-forward work per token, layer count and vocabulary (Kudazen
-    beside the Qwen3 decoder, Nazulorn beside Kudazen).  One JSON line."""
+    """--family kudazen | nazulorn | gulazen: the design at a few sizes that resemble a real model's layers (random weights),
+    beside the library's closest model of the same width, feed-forward work per token, layer count and vocabulary (Kudazen
+    beside the Qwen3 decoder, Nazulorn beside Kudazen, Gulazen beside Nazulorn).  One JSON line."""
     import torch
     peaks, peak_source = load_peaks()
     torch.cuda.set_device(0)
@@ -853,9 +875,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0)
     ap.add_argument("--skip-points", action="store_true", help="leave out the further decode points")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--family", default="", choices=["", "kudazen", "nazulorn"],
+    ap.add_argument("--family", default="", choices=["", "kudazen", "nazulorn", "gulazen"],
                     help="instead of the default workload: this model family at a few layer sizes, beside the library's closest "
-                         "model of equal size (kudazen beside the Qwen3 shape, nazulorn beside kudazen)")
+                         "model of equal size (kudazen beside the Qwen3 shape, nazulorn beside kudazen, gulazen beside nazulorn)")
     ap.add_argument("--sizes", default="", help="with --family: sizes to run, with commas between them (default: all)")
     args = ap.parse_args()
 

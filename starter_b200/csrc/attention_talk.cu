@@ -53,8 +53,11 @@ template <> __device__ __forceinline__ float talk_dot<__nv_bfloat16>(const float
 // One block per row.  Shared memory: the row's queries as floats [H * D], the table [H * H], raw and mixed scores of a
 // turn's 32 keys [H][32] each, the turn's key rows per key/value head [G][32], per head the running maximum and sum,
 // and the heads' value sums [H * V].  A warp takes heads warp, warp + warps, ...
+//
+// With n_splits > 1 (decoding: few rows, many keys) blockIdx.y takes a share of the row's turns and leaves, per head, its
+// unnormalised value sums, maximum and sum in ``partial`` [row][head][split][V + 2]; talking_merge_kernel divides.
 template <class T>
-__global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __restrict__ out) {
+__global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __restrict__ out, int n_splits, float* __restrict__ partial) {
     extern __shared__ __align__(16) unsigned char talk_sm[];
     const int H = p.n_heads, G = p.n_kv_heads, D = p.k_dim, V = p.v_dim, per_kv = H / G;
     long long* tok_s = reinterpret_cast<long long*>(talk_sm);            // [G][32]
@@ -83,9 +86,12 @@ __global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __r
     const int kept_end = min(p.keep_first, lo);       // kept first keys that the window does not hold anyway
     const T* kbase = (const T*)p.k;
     const T* vbase = (const T*)p.v;
-    for (int part = 0; part < 2; ++part) {
-        const int first = part == 0 ? 0 : lo, end = part == 0 ? kept_end : pos + 1;
-        for (int n0 = first; n0 < end; n0 += 32) {
+    const int kept_turns = (kept_end + 31) / 32, turns = kept_turns + (pos + 1 - lo + 31) / 32;
+    const int per_split = (turns + n_splits - 1) / n_splits;
+    const int turn_lo = blockIdx.y * per_split, turn_hi = min(turns, turn_lo + per_split);
+    {
+        for (int turn = turn_lo; turn < turn_hi; ++turn) {
+            const int n0 = turn < kept_turns ? turn * 32 : lo + (turn - kept_turns) * 32, end = turn < kept_turns ? kept_end : pos + 1;
             const int n = n0 + lane;
             const bool seen = n < end;
             for (int c = warp; c < G; c += n_warps) tok_s[c * 32 + lane] = seen ? flex_token(p, slot, n, c) : -1;
@@ -136,6 +142,17 @@ __global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __r
             __syncthreads();
         }
     }
+    if (n_splits > 1) {
+        for (int h = warp; h < H; h += n_warps) {
+            float* dst = partial + (((long long)row * H + h) * n_splits + blockIdx.y) * (V + 2);
+            for (int d = lane; d < V; d += 32) dst[d] = acc[h * V + d];
+            if (lane == 0) {
+                dst[V] = run_m[h];
+                dst[V + 1] = run_l[h];
+            }
+        }
+        return;
+    }
     for (int h = warp; h < H; h += n_warps) {
         float m = run_m[h], l = run_l[h], alpha = 1.f;
         if (p.sink != nullptr) {   // one more term in the denominator, no value behind it
@@ -147,6 +164,30 @@ __global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __r
         const float inv = alpha / l;
         T* orow = out + ((long long)row * H + h) * V;
         for (int d = lane; d < V; d += 32) orow[d] = from_f<T>(acc[h * V + d] * inv);
+    }
+}
+
+// One block per (row, head): the splits' sums, scaled to their common maximum (the sink's too), added and divided.
+template <class T>
+__global__ void talking_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, const float* __restrict__ sink, int n_heads,
+                                     int n_splits, int V) {
+    pdl_wait();
+    const long long rh = (long long)blockIdx.x * n_heads + blockIdx.y;
+    const float* base = partial + rh * n_splits * (V + 2);
+    float m = sink != nullptr ? sink[blockIdx.y] : -INFINITY;
+    for (int sidx = 0; sidx < n_splits; ++sidx) m = fmaxf(m, base[(long long)sidx * (V + 2) + V]);
+    float l = sink != nullptr ? expf(sink[blockIdx.y] - m) : 0.f;
+    for (int sidx = 0; sidx < n_splits; ++sidx) {
+        const float ms = base[(long long)sidx * (V + 2) + V];
+        if (ms != -INFINITY) l += base[(long long)sidx * (V + 2) + V + 1] * expf(ms - m);
+    }
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        float o = 0.f;
+        for (int sidx = 0; sidx < n_splits; ++sidx) {
+            const float ms = base[(long long)sidx * (V + 2) + V];
+            if (ms != -INFINITY) o = fmaf(base[(long long)sidx * (V + 2) + c], expf(ms - m), o);
+        }
+        out[rh * V + c] = from_f<T>(o / l);
     }
 }
 
@@ -210,8 +251,9 @@ long long sb_talking_attention_general_smem(int n_heads, int n_kv_heads, int k_d
                  * sizeof(float);
 }
 
-int sb_talking_attention_general(int dtype, SbFlex p, SbBatch batch, void* out, cudaStream_t stream) {
+int sb_talking_attention_general(int dtype, SbFlex p, SbBatch batch, void* out, int n_splits, float* partial, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
+    if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partial == nullptr)) return (int)cudaErrorInvalidValue;
     if (p.n_heads < 1 || p.n_kv_heads < 1 || p.n_heads % p.n_kv_heads || (p.v_heads > 0 && p.v_heads != p.n_kv_heads))
         return (int)cudaErrorInvalidValue;
     const long long smem = sb_talking_attention_general_smem(p.n_heads, p.n_kv_heads, p.k_dim, p.v_dim);
@@ -224,7 +266,11 @@ int sb_talking_attention_general(int dtype, SbFlex p, SbBatch batch, void* out, 
                 cudaFuncSetAttribute(talking_attention_general_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (err != cudaSuccess) return (int)err;                                                                               \
         }                                                                                                                          \
-        sb_launch(talking_attention_general_kernel<T>, batch.n_rows, 32 * warps, (size_t)smem, stream, p, batch, (T*)out);         \
+        sb_launch(talking_attention_general_kernel<T>, dim3(batch.n_rows, n_splits), 32 * warps, (size_t)smem, stream, p, batch,  \
+                  (T*)out, n_splits, partial);                                                                                     \
+        if (n_splits > 1)                                                                                                          \
+            sb_launch(talking_merge_kernel<T>, dim3(batch.n_rows, p.n_heads), 64, 0, stream, (const float*)partial, (T*)out,       \
+                      p.sink, p.n_heads, n_splits, p.v_dim);                                                                       \
     } while (0)
     if (dtype == SB_F32) SB_TALK(float);
     else SB_TALK(__nv_bfloat16);

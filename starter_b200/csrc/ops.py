@@ -145,7 +145,8 @@ class Ops:
             "sb_causal_conv": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, SbBatch, c_int, c_int, c_void_p, c_void_p],
             "sb_branch_norm_add": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
             "sb_xielu": [c_int, c_void_p, c_void_p, c_longlong, c_float, c_float, c_void_p],
-            "sb_talking_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_void_p],
+            "sb_talking_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_int, c_void_p, c_void_p],
+            "sb_talking_attention_mma": [SbFlex, SbBatch, c_void_p, c_int, c_void_p],
             "sb_qk_norm_store": [c_int, c_void_p, c_void_p, SbBatch, SbFlex, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
@@ -155,7 +156,7 @@ class Ops:
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
-        for fn in (lib.sb_flex_attention_mma_smem, lib.sb_flex_attention_rows64_smem):
+        for fn in (lib.sb_flex_attention_mma_smem, lib.sb_flex_attention_rows64_smem, lib.sb_talking_attention_mma_smem):
             fn.argtypes = [c_int, c_int, c_int, c_int]
             fn.restype = c_longlong
         lib.sb_set_pdl.argtypes = [c_int]
@@ -1214,9 +1215,45 @@ class Ops:
             raise KernelError("talking_attention: kept first keys go with a window")
         p = self._flex(layer_cache, q, H, scale, g.v_dim, False, sink, None, None, None, window, keep_first, softcap, talk)
         out = torch.empty((rows, H * g.v_dim), dtype=q.dtype, device=q.device)
-        self._check(self.lib.sb_talking_attention_general(_code(q.dtype), p, self._batch(ctx), _ptr(out), self._stream()),
-                    "talking_attention_general")
+        if self._talk_takes_mma(ctx, q, p):
+            self._check(self.lib.sb_talking_attention_mma(p, self._batch(ctx), _ptr(out), ctx.max_q_len, self._stream()),
+                        "talking_attention_mma")
+            return out
+        n_splits = self.talk_splits(ctx, p, g.table_width)
+        partial = None
+        if n_splits > 1:
+            key = ("talk_partial", q.device, rows, H, n_splits, g.v_dim)
+            partial = self._scratch.get(key)
+            if partial is None:
+                partial = self._scratch[key] = torch.empty(rows * H * n_splits * (g.v_dim + 2), dtype=torch.float32, device=q.device)
+        self._check(self.lib.sb_talking_attention_general(_code(q.dtype), p, self._batch(ctx), _ptr(out), n_splits, _ptr(partial),
+                                                          self._stream()), "talking_attention_general")
+        if n_splits > 1:
+            self.launches += 1   # the merge of the splits
         return out
+
+    TALK_PROMPT_MIN_ROWS = 4
+
+    def _talk_takes_mma(self, ctx, q, p: SbFlex) -> bool:
+        """The tensor-core kernel (16 positions with all their heads per block) takes bfloat16 steps in which a sequence
+        brings at least 4 rows, key widths that are multiples of 16, values of 64 or 128 columns, up to 32 heads (16 with
+        values of 128 columns) and rows it can fetch 16 bytes at a time; the block-per-row kernel serves everything else
+        (decoding, and every 32-bit run)."""
+        if not self.flex_tensor_cores or q.dtype != torch.bfloat16 or ctx.max_q_len < self.TALK_PROMPT_MIN_ROWS:
+            return False
+        smem = self.lib.sb_talking_attention_mma_smem(p.n_heads, p.n_kv_heads, p.k_dim, p.v_dim)
+        if smem < 0 or smem > self.MAX_BLOCK_SHARED:
+            return False
+        return q.stride(0) % 8 == 0 and q.stride(1) % 8 == 0 and q.data_ptr() % 16 == 0 and p.v_row % 8 == 0
+
+    def talk_splits(self, ctx, p: SbFlex, max_pages: int) -> int:
+        """Blocks along the keys per row of the block-per-row kernel: enough for two blocks per SM, none with less than
+        one turn of 32 keys.  A function of shapes only, so that a captured graph stays valid."""
+        reach = max_pages * 64
+        if p.window:
+            reach = min(reach, p.window + p.keep_first)
+        turns = max(1, (min(reach, ctx.kv_bound) + 31) // 32)
+        return max(1, min(-(-2 * self.sm_count() // max(1, ctx.n_rows)), turns, 64))
 
     # ---- sampling -----------------------------------------------------------------------
 

@@ -1,0 +1,558 @@
+"""Gulazen on the GPU against the plain implementation: every mechanism alone, then whole models in every way of
+cutting the work, keys at the edges of windows and pages and among the kept first tokens, a far key among hundreds,
+long decoding through a turning ring, and greedy generation through the entry point."""
+
+import pytest
+import torch
+
+import gulazen_cases as cases
+from conftest import random_tokens
+from helpers import assert_close, make_session, run_ragged_batches, run_tail_by_one, run_whole
+from plain import gulazen_plain as plain
+from starter_b200.cache import Cache
+from starter_b200.config import (ActMLPSpec, BranchNormSpec, CausalConvSpec, GatedMLPSpec, MoESpec, TalkingAttentionSpec)
+from starter_b200.engine import Engine
+from starter_b200.engine.context import Runtime, StepContext
+from starter_b200.parts import build_part
+
+pytestmark = pytest.mark.gpu
+MODES = ["float32", "bfloat16"]
+REL = {"float32": 3e-5, "bfloat16": 2.5e-2}
+
+
+def runtime(mode):
+    from starter_b200.csrc.ops import get_ops
+    return Runtime(dtype=getattr(torch, mode), device=torch.device("cuda"), ops=get_ops(verbose=False))
+
+
+def rand(shape, seed, scale=1.0, mean=0.0):
+    g = torch.Generator().manual_seed(seed)
+    return (mean + torch.randn(shape, generator=g) * scale).to(torch.bfloat16).float()   # bfloat16 numbers, so both modes read the same
+
+
+def close(got, want, mode, what, rel=None):
+    rel = rel or REL[mode]
+    scale = float(want.abs().max())
+    err = float((got.float().cpu() - want).abs().max())
+    assert err <= rel * scale, f"{what}: {err:.3g} > {rel * scale:.3g}"
+
+
+def context(rt, cache, slots, q_lens):
+    for s, n in zip(slots, q_lens):
+        cache.reserve(s, cache.lengths_host[s] + n)
+    cache.flush()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    row_seq = [b for b, n in enumerate(q_lens) for _ in range(n)]
+    return StepContext(runtime=rt, cache=cache, n_seqs=len(slots), n_rows=cu[-1], max_q_len=max(q_lens),
+                       kv_bound=max(cache.lengths_host[s] + n for s, n in zip(slots, q_lens)), seq_slot=i32(slots), cu_q=i32(cu),
+                       row_seq=i32(row_seq), lengths=cache.lengths, status=torch.zeros(1, dtype=torch.int32, device="cuda"))
+
+
+def run_part(rt, part, h, cuts, call, max_step_tokens=1024, pages=16, in_dtype=None):
+    """A part with a cache entry over one sequence whose rows h come in pieces of the given sizes: ``call(ctx, rows,
+    layer_cache)`` per piece; the outputs of all pieces in order, the cache and the slot."""
+    cache = Cache([part.cache_request()], n_slots=2, max_tokens=64 * pages, dtype=rt.dtype, device="cuda", max_step_tokens=max_step_tokens)
+    cache.alloc()                      # the sequence under test sits in the second slot
+    slot = cache.alloc()
+    outs, at = [], 0
+    pieces = [min(cache.step_limit, n - lo) for n in cuts for lo in range(0, n, cache.step_limit)]   # as the step function cuts
+    for n in pieces:
+        ctx = context(rt, cache, [slot], [n])
+        outs.append(call(ctx, h[at:at + n].to(in_dtype or rt.dtype).cuda().contiguous(), cache.layers[0]))
+        rt.ops.advance_lengths(ctx)
+        cache.advance_host(slot, n)
+        assert int(ctx.status.item()) == 0
+        at += n
+    return torch.cat(outs), cache, slot
+
+
+def cuttings(n):
+    """Whole; a tail token by token; portions of two; two unequal portions; every token alone."""
+    return [[n], [n - 9] + [1] * 9, [2] * (n // 2) + [1] * (n % 2), [n // 3, n - n // 3], [1] * n]
+
+
+# ---- the position vector ------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("width", [40, 96, 1030])
+def test_position_vector_is_added_in_32_bit(width):
+    rt = runtime("bfloat16")
+    table = rand((50, width), 1)
+    freqs = torch.tensor([10000.0 ** (-2.0 * i / width) for i in range((width + 1) // 2)], dtype=torch.float32)
+    cache = Cache([None], n_slots=2, max_tokens=64 * 80, dtype=rt.dtype, device="cuda")
+    a, b = cache.alloc(), cache.alloc()
+    cache.assume_length(b, 4990)           # far positions: the angle itself is a large 32-bit number there
+    ctx = context(rt, cache, [a, b], [5, 3])
+    tokens = torch.tensor([3, 49, 0, 3, 7, 1, 2, 3], dtype=torch.int32, device="cuda")
+    out = rt.ops.embed_sinusoid(ctx, tokens, table.to(rt.dtype).cuda(), freqs.cuda())
+    assert out.dtype == torch.float32 and int(ctx.status.item()) == 0
+    positions = torch.tensor([0, 1, 2, 3, 4, 4990, 4991, 4992])
+    want = table[tokens.long().cpu()] + plain.sinusoid(positions, width)
+    assert float((out.cpu() - want).abs().max()) <= 2e-3      # sin of an angle near 5000 moves by 5000 * 6e-8 with the angle's last bit
+    assert float((out.cpu()[:5] - want[:5]).abs().max()) <= 2e-6
+
+
+# ---- the short convolution ----------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("width, taps", [(96, 4), (40, 2), (1030, 5), (64, 1), (32, 3)])
+def test_short_convolution_alone(mode, width, taps):
+    rt = runtime(mode)
+    w = rand((width, taps), 2, 0.4)
+    part = build_part("conv", CausalConvSpec(size=width, taps=taps), {"weight": w.to(rt.dtype).cuda()}, rt)
+    n = 45
+    h = rand((n, width), 3) + 1e-4 * rand((n, width), 4)          # a 32-bit residual is no bfloat16 number
+    want = h + plain.causal_conv(h, w)
+    for cuts in cuttings(n):
+        cache = Cache([part.cache_request()], n_slots=2, max_tokens=64 * 4, dtype=rt.dtype, device="cuda")
+        cache.alloc()
+        slot = cache.alloc()
+        outs, at = [], 0
+        for m in cuts:
+            ctx = context(rt, cache, [slot], [m])
+            outs.append(part.forward(ctx, h[at:at + m].cuda().contiguous(), cache.layers[0]))
+            rt.ops.advance_lengths(ctx)
+            cache.advance_host(slot, m)
+            at += m
+        got = torch.cat(outs)
+        assert got.dtype == rt.dtype
+        close(got, want, mode, f"{taps} taps, cut {cuts[:3]}..", rel=2e-6 if mode == "float32" else 6e-3)
+
+
+def test_convolution_state_of_two_sequences_and_a_slot_used_again():
+    rt = runtime("float32")
+    width, taps = 48, 4
+    w = rand((width, taps), 5, 0.5)
+    part = build_part("conv", CausalConvSpec(size=width, taps=taps), {"weight": w.cuda()}, rt)
+    cache = Cache([part.cache_request()], n_slots=2, max_tokens=64 * 4, dtype=rt.dtype, device="cuda")
+    a, b = cache.alloc(), cache.alloc()
+    ha, hb = rand((9, width), 6), rand((4, width), 7)
+    wa, wb = ha + plain.causal_conv(ha, w), hb + plain.causal_conv(hb, w)
+    ctx = context(rt, cache, [a, b], [7, 2])                     # a ragged step, then one token each
+    got = part.forward(ctx, torch.cat([ha[:7], hb[:2]]).cuda(), cache.layers[0])
+    rt.ops.advance_lengths(ctx)
+    cache.advance_host(a, 7), cache.advance_host(b, 2)
+    close(got, torch.cat([wa[:7], wb[:2]]), "float32", "ragged step", rel=2e-6)
+    for step in range(2):
+        ctx = context(rt, cache, [a, b], [1, 1])
+        got = part.forward(ctx, torch.stack([ha[7 + step], hb[2 + step]]).cuda(), cache.layers[0])
+        rt.ops.advance_lengths(ctx)
+        cache.advance_host(a, 1), cache.advance_host(b, 1)
+        close(got, torch.stack([wa[7 + step], wb[2 + step]]), "float32", f"one token each, step {step}", rel=2e-6)
+    cache.free(a)
+    a2 = cache.alloc()                                           # the same slot: its record starts from zeros
+    assert a2 == a
+    ctx = context(rt, cache, [a2], [2])
+    got = part.forward(ctx, hb[:2].cuda().contiguous(), cache.layers[0])
+    close(got, wb[:2], "float32", "a slot used again", rel=2e-6)
+
+
+# ---- the norm of a branch's output, the two-sided activation -------------------------------------------------
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("width", [40, 96, 1030, 4104])
+def test_branch_norm_adds_into_the_32_bit_residual(mode, width):
+    rt = runtime(mode)
+    w, ls = rand((width,), 1, 0.2), rand((width,), 2, 0.2, 0.6)
+    part = build_part("norm", BranchNormSpec(size=width, eps=3e-5, offset=1.0, layer_scale=True),
+                      {"weight": w.to(rt.dtype).cuda(), "scale": ls.to(rt.dtype).cuda()}, rt)
+    x = rand((7, width), 3, 3.0) + 1e-4 * rand((7, width), 4)
+    y = rand((7, width), 5, 0.01)                                 # a small output: eps is felt
+    want = x + plain.one_plus_norm(y, w, 3e-5) * ls
+    xs = x.clone().cuda()
+    rounded = part.add_to(xs, y.to(rt.dtype).cuda(), want_rounded=True)
+    assert xs.dtype == torch.float32 and rounded.dtype == rt.dtype
+    close(xs, want, mode, "the residual stays 32-bit", rel=2e-6)
+    assert torch.equal(rounded.float(), xs.to(rt.dtype).float())
+    assert part.add_to(xs, y.to(rt.dtype).cuda()) is None
+    close(xs, want + plain.one_plus_norm(y, w, 3e-5) * ls, mode, "a second branch", rel=2e-6)
+    w1 = (1.0 + w).to(torch.bfloat16).float()
+    bare = build_part("norm", BranchNormSpec(size=width, eps=1e-6), {"weight": w1.to(rt.dtype).cuda()}, rt)
+    xs = x.clone().cuda()
+    bare.add_to(xs, y.to(rt.dtype).cuda())
+    close(xs, x + plain.unit_rms(y, 1e-6) * w1, mode, "no offset, no layer scale", rel=2e-6)
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("pq", [(0.3, -0.2), (-2.0, 1.5), (0.0, 0.0)])
+def test_two_sided_activation(mode, pq):
+    rt = runtime(mode)
+    z = torch.cat([rand((3, 333), 1, 2.0), torch.tensor([[0.0, -0.0, 1e-4, -1e-4, 20.0, -20.0, -90.0] + [0.5] * 326])]).to(torch.bfloat16).float()
+    want = plain.xielu(z, torch.tensor(pq[0]), torch.tensor(pq[1]))
+    sp = torch.nn.functional.softplus(torch.tensor(pq))
+    got = rt.ops.xielu(z.to(rt.dtype).cuda(), float(sp[0]), 0.5 + float(sp[1]))
+    if mode == "float32":
+        assert float((got.cpu() - want).abs().max()) <= 1e-5 * float(want.abs().max())
+        assert float((got.cpu() - want)[want.abs() < 1].abs().max()) <= 2e-6      # near zero exp(z) - 1 - z must not lose its digits
+    else:
+        assert torch.equal(got.float().cpu(), want.to(torch.bfloat16).float()) or float(((got.float().cpu() - want).abs() / (want.abs() + 1e-3)).max()) <= 8e-3
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("width, ff", [(96, 136), (40, 52), (1024, 2048)])
+def test_dense_feed_forward_alone(mode, width, ff):
+    rt = runtime(mode)
+    w = {"up": rand((ff, width), 1, width ** -0.5), "down": rand((width, ff), 2, ff ** -0.5), "act": torch.tensor([0.4, -0.3]).to(torch.bfloat16).float()}
+    part = build_part("ff", ActMLPSpec(hidden_size=width, intermediate_size=ff), {k: v.to(rt.dtype).cuda() for k, v in w.items()}, rt)
+    h = rand((21, width), 3)
+    close(part.forward(None, h.to(rt.dtype).cuda()), plain.dense_ff(h, w), mode, "dense")
+    close(part.forward(None, h[:1].to(rt.dtype).cuda().contiguous()), plain.dense_ff(h[:1], w), mode, "one row")
+
+
+# ---- the experts ------------------------------------------------------------------------------------------
+
+def moe_weights(E, width, ff, shared, seed):
+    w = {"router": rand((E, width), seed, 2.0 * width ** -0.5), "router.b": rand((E,), seed + 1, 0.5)}
+    for e in range(E):
+        w.update({f"e{e}.gate": rand((ff, width), seed + 10 + 3 * e, width ** -0.5), f"e{e}.up": rand((ff, width), seed + 11 + 3 * e, width ** -0.5),
+                  f"e{e}.down": rand((width, ff), seed + 12 + 3 * e, ff ** -0.5)})
+    if shared:
+        w.update({"shared.gate": rand((shared, width), seed + 2, width ** -0.5), "shared.up": rand((shared, width), seed + 3, width ** -0.5),
+                  "shared.down": rand((width, shared), seed + 4, shared ** -0.5)})
+    return w
+
+
+def moe_part(rt, E, top, width, ff, shared, w):
+    gated = lambda n: GatedMLPSpec(hidden_size=width, intermediate_size=n, activation="silu")
+    spec = MoESpec(hidden_size=width, n_experts=E, n_identity=0, top=top, route_scale=1.0, expert=gated(ff),
+                   shared=gated(shared) if shared else None, router_bias=True, correction=False, over_chosen=True)
+    named = {k.replace("router.b", "router_bias").replace(".", "_"): v.to(rt.dtype).cuda() for k, v in w.items()}
+    return build_part("ff", spec, named, rt)
+
+
+@pytest.mark.parametrize("E, top, width, ff, shared", [(5, 3, 96, 40, 56), (4, 1, 96, 72, 0), (3, 3, 128, 80, 96), (2, 2, 40, 24, 16),
+                                                        (16, 4, 256, 128, 192)])
+def test_router_takes_the_largest_logits_and_weighs_over_them(E, top, width, ff, shared):
+    rt = runtime("float32")
+    w = moe_weights(E, width, ff, shared, 40)
+    part = moe_part(rt, E, top, width, ff, shared, w)
+    h = rand((33, width), 7)
+    chosen, weight = rt.ops.moe_route(h.cuda(), part.router, None, top, 1.0, bias=part.bias, over_chosen=True)
+    want_chosen, want_weight = plain.route(h, w, top)
+    order = chosen.long().cpu().argsort(dim=1)
+    want_order = want_chosen.argsort(dim=1)
+    assert torch.equal(chosen.long().cpu().gather(1, order), want_chosen.gather(1, want_order))
+    assert float((weight.cpu().gather(1, order) - want_weight.gather(1, want_order)).abs().max()) <= 2e-6
+    assert float((weight.sum(1) - 1).abs().max()) <= 1e-6         # over the chosen ones only: they sum to one
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("E, top, width, ff, shared", [(5, 3, 96, 40, 56), (4, 1, 96, 72, 0), (3, 3, 128, 80, 96), (2, 2, 40, 24, 16),
+                                                        (16, 4, 256, 128, 192)])
+def test_experts_alone(mode, E, top, width, ff, shared):
+    rt = runtime(mode)
+    w = moe_weights(E, width, ff, shared, 60)
+    part = moe_part(rt, E, top, width, ff, shared, w)
+    mlp = {"router": {"experts": E, "top": top}, "shared": {"ff": shared} if shared else None}
+    for rows in (1, 2, 37):
+        h = rand((rows, width), 8 + rows)
+        close(part.forward(None, h.to(rt.dtype).cuda()), plain.moe_ff(h, w, mlp), mode, f"{rows} rows")
+
+
+def test_a_large_bias_decides_the_choice():
+    """The bias enters the choice AND the weights: one expert's bias far above the others makes it every token's first."""
+    rt = runtime("float32")
+    w = moe_weights(6, 64, 32, 0, 80)
+    w["router.b"] = torch.tensor([0.0, 0.0, 0.0, 20.0, 0.0, 0.0])
+    part = moe_part(rt, 6, 2, 64, 32, 0, w)
+    h = rand((20, 64), 3)
+    chosen, weight = rt.ops.moe_route(h.cuda(), part.router, None, 2, 1.0, bias=part.bias, over_chosen=True)
+    best = weight.argmax(dim=1, keepdim=True)
+    assert bool((chosen.long().gather(1, best) == 3).all()) and float(weight.max(dim=1).values.min()) > 0.9
+    close(part.forward(None, h.cuda()), plain.moe_ff(h, w, {"router": {"experts": 6, "top": 2}}), "float32", "output")
+
+
+# ---- attention whose scores meet across heads ---------------------------------------------------------------
+
+def talk_spec(H, G, D, V, window=None, keep=0, softcap=None, scale=None, talk=True, sink=True, norm=True, width=80):
+    return TalkingAttentionSpec(hidden_size=width, num_heads=H, num_kv_heads=G, head_dim=D, v_dim=V, scale=D ** -0.5 if scale is None else scale,
+                                qk_norm_eps=1e-5 if norm else None, softcap=softcap, talk=talk, sink=sink, window=window, keep_first=keep)
+
+
+def talk_weights(s, seed):
+    H, G, D, V, h = s.num_heads, s.num_kv_heads, s.head_dim, s.v_dim, s.hidden_size
+    w = {"q": rand((H * D, h), seed, h ** -0.5), "k": rand((G * D, h), seed + 1, h ** -0.5), "v": rand((G * V, h), seed + 2, h ** -0.5),
+         "o": rand((h, H * V), seed + 3, (H * V) ** -0.5)}
+    if s.qk_norm_eps is not None:
+        w.update({"q.norm": rand((H * D,), seed + 4, 0.2, 1.5), "k.norm": rand((G * D,), seed + 5, 0.2, 1.5)})
+    if s.talk:
+        w["talk"] = rand((H, H), seed + 6, 0.3) + torch.eye(H)
+    if s.sink:
+        w["sink"] = rand((H,), seed + 7, 1.0)
+    return w
+
+
+def talk_entry(s):
+    m = {"heads": s.num_heads, "kv_heads": s.num_kv_heads, "dim": s.head_dim, "vdim": s.v_dim, "scale": s.scale}
+    if s.softcap is not None:
+        m["softcap"] = s.softcap
+    if s.window is not None:
+        m["mask"] = {"size": s.window, "keep_first": s.keep_first}
+    return m
+
+
+def talk_part(rt, s, w):
+    return build_part("mixer", s, {k.replace(".", "_"): v.to(rt.dtype).cuda() for k, v in w.items()}, rt)
+
+
+def plain_attention(h, w, s):
+    if s.qk_norm_eps is None:                                     # the plain function always norms: ones and no eps stand for none
+        raise AssertionError("the plain attention norms its queries and keys")
+    return plain.attention(h, w, talk_entry(s), s.qk_norm_eps)
+
+
+def run_mixer(rt, part, h, cuts, max_step_tokens=1024, pages=16):
+    return run_part(rt, part, h, cuts, part.forward, max_step_tokens, pages)
+
+
+TALK_SIZES = [
+    dict(H=6, G=2, D=16, V=24, window=20, keep=3, softcap=8.0, scale=0.4),     # the general kernel
+    dict(H=8, G=2, D=32, V=64, window=64, keep=5, softcap=20.0),               # sizes the tensor-core kernel takes; a window of one page
+    dict(H=2, G=1, D=64, V=128, window=100, keep=70, softcap=30.0, scale=0.2), # kept tokens beyond the first page
+    dict(H=1, G=1, D=20, V=12, window=None, softcap=5.0),                      # one head: the table is one number
+    dict(H=16, G=4, D=64, V=64, window=70, keep=64),                           # no cap; a whole page kept
+    dict(H=16, G=8, D=128, V=128, window=33, keep=1, softcap=50.0),
+    dict(H=4, G=4, D=64, V=64, window=130, keep=2, softcap=10.0),              # as many key/value heads as query heads
+    dict(H=3, G=3, D=32, V=64, window=7, keep=9, softcap=3.0),                 # more kept tokens than the window is long
+    dict(H=12, G=3, D=48, V=64, window=40, keep=0, softcap=15.0),              # a window that keeps nothing
+    dict(H=8, G=2, D=64, V=64, window=50, keep=4, softcap=30.0, talk=False),   # options off, one at a time
+    dict(H=8, G=2, D=64, V=64, window=50, keep=4, softcap=30.0, sink=False),
+    dict(H=32, G=8, D=64, V=64, window=90, keep=6, softcap=25.0),
+]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("sizes", TALK_SIZES)
+def test_talking_attention_alone(mode, sizes):
+    rt = runtime(mode)
+    spec = talk_spec(**sizes)
+    w = talk_weights(spec, 20)
+    part = talk_part(rt, spec, w)
+    n = 150
+    h = rand((n, spec.hidden_size), 3)
+    want = plain_attention(h, w, spec)
+    for cuts in cuttings(n):
+        got, _, _ = run_mixer(rt, part, h, cuts, max_step_tokens=48)            # rings of pages wrap; steps of 48 rows at most
+        close(got, want, mode, f"cut {cuts[:3]}..")
+
+
+def standout(spec, n, at, seed, strength=6.0):
+    """Rows and weights in which the keys at the positions ``at`` stand out for every query of head 0: ordinary rows share
+    a direction u and have nothing along a second direction z; the rows at ``at`` are a multiple of z; the first key
+    head's matrix maps z onto what the first query head makes of u.  The values at ``at`` are large with the rows, so
+    that seeing or not seeing such a key moves the output."""
+    w = talk_weights(spec, seed)
+    D = spec.head_dim
+    u, z = rand((spec.hidden_size,), seed + 50), rand((spec.hidden_size,), seed + 51)
+    z = z - u * float(z @ u) / float(u @ u)
+    noise = rand((n, spec.hidden_size), seed + 52, 0.3)
+    noise = noise - torch.outer(noise @ z, z) / float(z @ z)
+    h = noise + 0.5 * u
+    for j in at:
+        h[j] = strength * z
+    w["k"][:D] += 3.0 * torch.outer(w["q"][:D] @ u, z) / float(z @ z)
+    w["k"] = w["k"].to(torch.bfloat16).float()
+    return h.to(torch.bfloat16).float(), w
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("sizes, n, key", [
+    (dict(H=4, G=2, D=32, V=64, window=37, keep=0, softcap=30.0), 140, 20),     # the window's edge passes the key
+    (dict(H=8, G=2, D=64, V=64, window=64, keep=0, softcap=30.0), 200, 63),     # ... a key at the end of a page, a window of a page
+    (dict(H=8, G=2, D=64, V=64, window=65, keep=0, softcap=30.0), 200, 64),     # ... at the start of a page
+    (dict(H=6, G=2, D=16, V=24, window=5, keep=0, softcap=30.0), 80, 2),
+    (dict(H=8, G=2, D=64, V=64, window=16, keep=4, softcap=30.0), 400, 3),      # the last kept token, seen from hundreds of tokens away
+    (dict(H=8, G=2, D=64, V=64, window=16, keep=4, softcap=30.0), 400, 4),      # the first one that is not kept
+    (dict(H=2, G=1, D=64, V=128, window=10, keep=65, softcap=30.0), 300, 64),   # kept, in the second page
+    (dict(H=2, G=1, D=64, V=128, window=10, keep=65, softcap=30.0), 300, 65),
+    (dict(H=16, G=4, D=64, V=64, window=None, softcap=30.0), 700, 1),           # no window: a far key among hundreds
+])
+def test_a_key_that_stands_out_at_the_edges(mode, sizes, n, key):
+    rt = runtime(mode)
+    spec = talk_spec(**sizes)
+    h, w = standout(spec, n, [key], 70)
+    part = talk_part(rt, spec, w)
+    want = plain_attention(h, w, spec)
+    if spec.window is not None and key >= spec.keep_first:
+        edge = key + spec.window                                               # the first query that no longer sees the key
+        moved = float((want[edge - 1] - want[edge]).abs().max())
+        assert moved > 0.2 * float(want.abs().max()), "the test's key does not stand out"
+    for cuts in ([n], [n // 2] + [1] * (n - n // 2), [n - 1, 1]):
+        got, _, _ = run_mixer(rt, part, h, cuts, max_step_tokens=64, pages=24)
+        close(got, want, mode, f"key {key}, cut {cuts[:2]}..")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_the_sink_takes_its_share(mode):
+    rt = runtime(mode)
+    spec = talk_spec(H=4, G=2, D=32, V=64, window=30, keep=2, softcap=10.0)
+    w = talk_weights(spec, 90)
+    h = rand((50, spec.hidden_size), 4)
+    w["sink"] = torch.tensor([12.0, -30.0, 0.0, 40.0])           # above the cap's reach (before mixing), far below, level, far above
+    want = plain_attention(h, w, spec)
+    got, _, _ = run_mixer(rt, talk_part(rt, spec, w), h, [50])
+    close(got, want, mode, "sinks of every size")
+    w2 = dict(w)
+    w2.pop("sink")
+    without = plain.attention(h, w2, talk_entry(spec), 1e-5)
+    assert float((without - want).abs().max()) > 0.3 * float(without.abs().max())
+    # the first token: one key and the sink
+    got, _, _ = run_mixer(rt, talk_part(rt, spec, w), h[:1], [1])
+    close(got, want[:1], mode, "a sequence's first token")
+
+
+def test_mixing_reaches_across_key_value_groups():
+    """Head 0's new score is all of head 5's old one: a table that is a permutation moves a pattern from one group to another."""
+    rt = runtime("float32")
+    spec = talk_spec(H=6, G=3, D=16, V=8, window=None, softcap=6.0)
+    w = talk_weights(spec, 110)
+    perm = torch.tensor([5, 4, 3, 2, 1, 0])
+    w["talk"] = torch.eye(6)[perm]
+    h = rand((40, spec.hidden_size), 5)
+    got, _, _ = run_mixer(rt, talk_part(rt, spec, w), h, [40])
+    close(got, plain_attention(h, w, spec), "float32", "a permutation of the heads' scores")
+    w2 = dict(w, talk=torch.eye(6))
+    assert float((plain_attention(h, w2, spec) - plain_attention(h, w, spec)).abs().max()) > 0.05
+
+
+# ---- whole models -------------------------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name in cases.CASES:
+        out[name, "bfloat16"] = cases.write_folder(name, tmp_path_factory.mktemp(f"gulazen_{name}_bf16"))
+        out[name, "float32"] = cases.write_folder(name, tmp_path_factory.mktemp(f"gulazen_{name}_f32"), dtype=torch.float32, shards=2)
+    return out
+
+
+def model_close(got, ref, mode, what, name=None, share=0.9):
+    """32-bit runs: every position within the tolerance.  bfloat16 runs of a model that chooses among experts: a router's
+    close call may fall the other way after rounding and move that position's logits altogether, and the positions whose
+    window holds it a little; so most positions stay within the tolerance and none strays far.  What a wrong key, state or
+    page does shows in the 32-bit run of the same cutting."""
+    routed = name is None or any((e.get("mlp") or {}).get("kind") == "moe" and e["mlp"]["router"]["top"] < e["mlp"]["router"]["experts"]
+                                 for e in cases.CASES[name]["layers"])
+    if mode == "float32" or not routed:
+        return assert_close(got, ref, mode, what)
+    from helpers import TOLERANCE
+    scale = max(float(r.abs().max()) for r in ref)
+    for g, r in zip(got, ref):
+        assert g.shape == r.shape
+    errs = torch.cat([(g - r).abs().max(dim=1).values for g, r in zip(got, ref)]) / scale
+    within = float((errs <= TOLERANCE[mode]).float().mean())
+    assert within >= share and float(errs.max()) < 0.7, f"{what}: {within:.2f} of the positions within the tolerance, worst {float(errs.max()):.3g}"
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_every_cutting_matches_plain(folders, name, mode):
+    folder = folders[name, mode]
+    seqs = random_tokens(cases.CASES[name]["vocab"], (5, 90, 41, 1, 64, 65, 2, 150), seed=3)
+    ref = cases.plain_logits(folder, seqs)
+    sess = make_session(folder, mode, max_tokens=64 * 16, max_seqs=4, max_step_tokens=24, max_rows=50)   # prompts in portions of 24
+    model_close(run_whole(sess, seqs), ref, mode, "alone and whole", name)
+    model_close(run_whole(sess, seqs[:3], together=True), ref[:3], mode, "one ragged step", name)
+    model_close(run_tail_by_one(sess, seqs, tail=40), ref, mode, "tail one by one", name)
+    model_close(run_ragged_batches(sess, seqs, batch_size=3, poison=True), ref, mode, "ragged batches, freed pages poisoned", name)
+    assert sess.cache.slots.n_held == 0
+    wide = make_session(folder, mode, max_tokens=64 * 16, max_seqs=4)                                   # prompts whole
+    model_close(run_whole(wide, seqs), ref, mode, "whole prompts in one step", name)
+    model_close(run_whole(wide, seqs[4:], together=True), ref[4:], mode, "unequal requests in one step", name)
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_portions_down_to_two_tokens(folders, mode):
+    name = "A"
+    seqs = random_tokens(211, (37,), seed=4)
+    ref = cases.plain_logits(folders["A", mode], seqs)
+    for portion in (2, 3, 7, 21):
+        sess = make_session(folders["A", mode], mode, max_tokens=64 * 4, max_seqs=2, max_step_tokens=portion)
+        model_close(run_whole(sess, seqs), ref, mode, f"portions of {portion}", name)
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_the_ring_turns_under_the_pinned_pages(folders, mode):
+    name = "B"
+    seqs = random_tokens(300, (700,), seed=12)
+    ref = cases.plain_logits(folders["B", mode], seqs)
+    sess = make_session(folders["B", mode], mode, max_tokens=64 * 30, max_seqs=2, max_seq_tokens=64 * 16, max_step_tokens=16)
+    g = sess.cache.layers[1].group
+    assert g.pinned_pages == 2 and g.table_width < 700 // 64
+    model_close(run_tail_by_one(sess, seqs, tail=300), ref, mode, "long decoding through a turning ring", name)
+    model_close(run_whole(sess, seqs), ref, mode, "a long prompt in portions through a turning ring", name)
+
+
+def test_layers_match_plain(folders):
+    cfg, tensors = plain.read_folder(folders["A", "float32"])
+    tokens = random_tokens(211, (19,), seed=9)[0]
+    want = []
+    plain.forward(cfg, tensors, tokens, want)
+    sess = make_session(folders["A", "float32"], "float32", max_tokens=64 * 4, max_seqs=2)
+    seen = []
+    for block in sess.model.blocks:
+        inner = block.forward
+
+        def spy(ctx, stream, layer_cache, inner=inner):
+            inner(ctx, stream, layer_cache)
+            seen.append(stream.x.clone())
+        block.forward = spy
+    run_whole(sess, [tokens])
+    assert len(seen) == len(want) == 4
+    for i, (got, ref) in enumerate(zip(seen, want)):
+        assert got.dtype == torch.float32
+        assert float((got.cpu() - ref).abs().max()) <= 2e-5 * float(ref.abs().max()), f"layer {i}"
+
+
+def test_the_residual_is_32_bit_in_a_bfloat16_run(folders):
+    sess = make_session(folders["D", "bfloat16"], "bfloat16", max_tokens=64 * 4, max_seqs=2)
+    kinds = []
+    for block in sess.model.blocks:
+        inner = block.forward
+
+        def spy(ctx, stream, layer_cache, inner=inner):
+            inner(ctx, stream, layer_cache)
+            kinds.append(stream.x.dtype)
+        block.forward = spy
+    run_whole(sess, random_tokens(64, (9,), seed=1))
+    assert kinds == [torch.float32] * 2
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_greedy_generation_through_the_entry_point(folders, mode):
+    cfg, tensors = plain.read_folder(folders["C", "float32"])
+    prompts = random_tokens(97, (3, 11, 1, 30), seed=6)
+    want = plain.generate(cfg, tensors, prompts, 12)
+    engine = Engine.from_session(make_session(folders["C", "float32"], "float32", max_tokens=64 * 8, max_seqs=4))   # graphs on
+    assert engine.generate_all(prompts, 12) == want
+    assert engine.session.cache.slots.n_held == 0
+    if mode == "bfloat16":      # rounding may turn a close call: the first tokens agree, and every request ends
+        engine = Engine.from_session(make_session(folders["C", "bfloat16"], "bfloat16", max_tokens=64 * 8, max_seqs=4))
+        got = engine.generate_all(prompts, 12)
+        assert [len(g) for g in got] == [12] * 4 and engine.session.cache.slots.n_held == 0
+
+
+def test_the_trace_runner_replays_this_design(folders, tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    import numpy as np
+    root = Path(__file__).resolve().parent.parent
+    folder = folders["D", "float32"]
+    seqs = random_tokens(64, (20, 9), seed=2)
+    ref = cases.plain_logits(folder, seqs)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": seqs[0][:15], "want": [14]}, {"id": "b", "tokens": seqs[1][:8], "want": [0, 7]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": seqs[0][15:16], "want": [0]}, {"id": "b", "tokens": seqs[1][8:9], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": seqs[0][16:17], "want": []}], "end": []},
+             {"step": 3, "entries": [{"id": "a", "tokens": seqs[0][17:20], "want": [2]}], "end": ["a"]}]
+    proc = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path),
+                           "--max-tokens", "64"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"] and not (tmp_path / "2.f32").exists()
+    read = lambda i: torch.from_numpy(np.fromfile(tmp_path / f"{i}.f32", dtype="<f4").reshape(-1, 64).copy())
+    want = {0: torch.stack([ref[0][14], ref[1][0], ref[1][7]]), 1: torch.stack([ref[0][15], ref[1][8]]), 3: ref[0][19:20]}
+    for i, r in want.items():
+        assert float((read(i) - r).abs().max()) <= 1e-4 * float(r.abs().max()), f"step {i}"
