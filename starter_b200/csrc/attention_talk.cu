@@ -242,6 +242,12 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
     }
 }
 
+void sb_talking_merge_bf16(const float* partial, void* out, const float* sink, int n_rows, int n_heads, int n_splits, int v_dim,
+                           cudaStream_t stream) {
+    sb_launch(talking_merge_kernel<__nv_bfloat16>, dim3(n_rows, n_heads), 64, 0, stream, partial, (__nv_bfloat16*)out, sink, n_heads,
+              n_splits, v_dim);
+}
+
 extern "C" {
 
 // Bytes of shared memory the general kernel asks for.

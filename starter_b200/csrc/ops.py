@@ -146,7 +146,7 @@ class Ops:
             "sb_branch_norm_add": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
             "sb_xielu": [c_int, c_void_p, c_void_p, c_longlong, c_float, c_float, c_void_p],
             "sb_talking_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_int, c_void_p, c_void_p],
-            "sb_talking_attention_mma": [SbFlex, SbBatch, c_void_p, c_int, c_void_p],
+            "sb_talking_attention_mma": [SbFlex, SbBatch, c_void_p, c_int, c_int, c_void_p, c_void_p],
             "sb_qk_norm_store": [c_int, c_void_p, c_void_p, SbBatch, SbFlex, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
@@ -1215,19 +1215,20 @@ class Ops:
             raise KernelError("talking_attention: kept first keys go with a window")
         p = self._flex(layer_cache, q, H, scale, g.v_dim, False, sink, None, None, None, window, keep_first, softcap, talk)
         out = torch.empty((rows, H * g.v_dim), dtype=q.dtype, device=q.device)
-        if self._talk_takes_mma(ctx, q, p):
-            self._check(self.lib.sb_talking_attention_mma(p, self._batch(ctx), _ptr(out), ctx.max_q_len, self._stream()),
-                        "talking_attention_mma")
-            return out
-        n_splits = self.talk_splits(ctx, p, g.table_width)
+        mma = self._talk_takes_mma(ctx, q, p)
+        n_splits = self.talk_mma_splits(ctx, p, g.table_width) if mma else self.talk_splits(ctx, p, g.table_width)
         partial = None
         if n_splits > 1:
             key = ("talk_partial", q.device, rows, H, n_splits, g.v_dim)
             partial = self._scratch.get(key)
             if partial is None:
                 partial = self._scratch[key] = torch.empty(rows * H * n_splits * (g.v_dim + 2), dtype=torch.float32, device=q.device)
-        self._check(self.lib.sb_talking_attention_general(_code(q.dtype), p, self._batch(ctx), _ptr(out), n_splits, _ptr(partial),
-                                                          self._stream()), "talking_attention_general")
+        if mma:
+            self._check(self.lib.sb_talking_attention_mma(p, self._batch(ctx), _ptr(out), ctx.max_q_len, n_splits, _ptr(partial),
+                                                          self._stream()), "talking_attention_mma")
+        else:
+            self._check(self.lib.sb_talking_attention_general(_code(q.dtype), p, self._batch(ctx), _ptr(out), n_splits, _ptr(partial),
+                                                              self._stream()), "talking_attention_general")
         if n_splits > 1:
             self.launches += 1   # the merge of the splits
         return out
@@ -1254,6 +1255,17 @@ class Ops:
             reach = min(reach, p.window + p.keep_first)
         turns = max(1, (min(reach, ctx.kv_bound) + 31) // 32)
         return max(1, min(-(-2 * self.sm_count() // max(1, ctx.n_rows)), turns, 64))
+
+    def talk_mma_splits(self, ctx, p: SbFlex, max_pages: int) -> int:
+        """Blocks along the keys per 16 positions of the tensor-core kernel: one block holds an SM (its scores of all heads
+        fill the shared memory), so a step of few positions with many keys in reach is cut until there are two blocks per
+        SM, none with less than 128 keys, four at most."""
+        reach = max_pages * 64
+        if p.window:
+            reach = min(reach, p.window + p.keep_first + 16)
+        reach = min(reach, ctx.kv_bound)
+        blocks = ctx.n_seqs * -(-ctx.max_q_len // 16)
+        return max(1, min(-(-2 * self.sm_count() // max(1, blocks)), reach // 128, 4))
 
     # ---- sampling -----------------------------------------------------------------------
 

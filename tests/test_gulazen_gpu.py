@@ -385,6 +385,26 @@ def test_a_key_that_stands_out_at_the_edges(mode, sizes, n, key):
 
 
 @pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("sizes", [
+    dict(H=16, G=8, D=128, V=128, window=300, keep=5, softcap=30.0),      # sixteen warps, wide values
+    dict(H=32, G=8, D=64, V=64, window=None, softcap=20.0),               # two heads per warp, no window
+    dict(H=12, G=4, D=32, V=64, window=520, keep=130, softcap=40.0),      # kept tokens over three pages, a window longer than a share
+])
+def test_a_long_prompt_whose_keys_are_shared_out_among_blocks(mode, sizes):
+    """Prompts of hundreds of tokens in one or two steps: few blocks of positions, each cut along its keys, and the shares
+    merged with the sink; every share's first and last tile, tiles nobody masks and tiles at the window's edge."""
+    rt = runtime(mode)
+    spec = talk_spec(**sizes)
+    w = talk_weights(spec, 130)
+    n = 610
+    h = rand((n, spec.hidden_size), 8)
+    want = plain_attention(h, w, spec)
+    for cuts in ([n], [333, n - 333]):
+        got, _, _ = run_mixer(rt, talk_part(rt, spec, w), h, cuts, max_step_tokens=1024, pages=24)
+        close(got, want, mode, f"cut {cuts}")
+
+
+@pytest.mark.parametrize("mode", MODES)
 def test_the_sink_takes_its_share(mode):
     rt = runtime(mode)
     spec = talk_spec(H=4, G=2, D=32, V=64, window=30, keep=2, softcap=10.0)
