@@ -57,6 +57,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// The two-sided activation: a_pos z^2 + z / 2 for z > 0, a_neg (exp(z) - 1 - z) + z / 2 otherwise.
+__device__ __forceinline__ float xielu_value(float v, float a_pos, float a_neg) {
+    return v > 0.f ? fmaf(a_pos * v, v, 0.5f * v) : fmaf(a_neg, expm1f(v) - v, 0.5f * v);
+}
+
 // Two 32-bit operations in one instruction (sm_100): a * b + c and a + b on pairs, each element rounded as the single
 // operation rounds it; and the largest of three.  For loops whose time is their instruction count.
 __device__ __forceinline__ float2 fma_pair(float2 a, float2 b, float2 c) {

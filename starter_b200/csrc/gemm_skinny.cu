@@ -50,6 +50,14 @@ int sb_gemm_skinny_gated(const void* A, const void* W, void* C, int M, int n_out
                                    SbSkinnyNorm{nullptr, 0.f, nullptr, 0, alpha, limit}, nullptr, partial, counters, stream);
 }
 
+// A plain product with the two-sided activation in the epilogue: xielu(A W^T), a_pos z^2 + z / 2 for z > 0,
+// a_neg (exp(z) - 1 - z) + z / 2 otherwise, z the product as it reads back from bfloat16.
+int sb_gemm_skinny_xielu(const void* A, const void* W, void* C, int M, int n_out, int K, int n_splits, int k_per_split, int tiled,
+                         int warps, float a_pos, float a_neg, float* partial, int* counters, cudaStream_t stream) {
+    return skinny_launch<false, 4>(A, W, C, M, n_out, K, n_splits, k_per_split, 0, 0, tiled, warps, 0,
+                                   SbSkinnyNorm{nullptr, 0.f, nullptr, 0, a_pos, 0.f, a_neg, 1}, nullptr, partial, counters, stream);
+}
+
 // The tile-major copy of a row-major matrix for the kernel above.  src [halves * rows, K] bfloat16 row-major; dst
 // holds halves * ceil(rows / 16) * ceil(K / 128) tiles of 16 x 128 (sb_tile_matrix_elements of them in all).
 long long sb_tile_matrix_elements(int rows, int K, int halves) {

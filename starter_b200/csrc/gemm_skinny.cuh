@@ -91,6 +91,10 @@ struct SbSkinnyNorm {
     // and u' = clamp(u, -limit, limit); 0 (what an initialiser that stops earlier leaves) the plain silu(g) * u
     float act_alpha;
     float act_limit;
+    // what the epilogue of a plain product computes when act_unary is set: the two-sided activation xielu_value(v,
+    // act_alpha, act_neg) of the product as it reads back from bfloat16
+    float act_neg;
+    int act_unary;
 };
 
 // Stores one output and returns what C now holds there.
@@ -301,6 +305,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
                     if (GATE_UP) v2 += *cluster.map_shared_rank(&red[WPG][r][m], c);
                 }
                 if (GATE_UP) v = gated_act(v, v2, norm.act_alpha, norm.act_limit);
+                else if (norm.act_unary) v = xielu_value(__bfloat162float(__float2bfloat16_rn(v)), norm.act_alpha, norm.act_neg);
                 stored = skinny_store(C, (long long)m * n_out + n0 + r, v, out_f32, accumulate);
             }
             if (stats_out != nullptr) skinny_leave_stats(stats_out, stored, m < M, m, r);
@@ -335,6 +340,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         if (m < M && n0 + r < n_out) {
             float v = red[0][r][m];
             if (GATE_UP) v = gated_act(v, red[WPG][r][m], norm.act_alpha, norm.act_limit);
+            else if (norm.act_unary) v = xielu_value(__bfloat162float(__float2bfloat16_rn(v)), norm.act_alpha, norm.act_neg);
             stored = skinny_store(C, (long long)m * n_out + n0 + r, v, out_f32, accumulate);
         }
         if (stats_out != nullptr) skinny_leave_stats(stats_out, stored, m < M, m, r);

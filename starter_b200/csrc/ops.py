@@ -91,6 +91,8 @@ class Ops:
                                c_int, c_void_p, c_void_p, c_void_p, c_void_p],
             "sb_gemm_skinny_gated": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
                                      c_void_p, c_void_p, c_void_p],
+            "sb_gemm_skinny_xielu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                     c_void_p, c_void_p, c_void_p],
             "sb_gemm_skinny_normed": [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
             "sb_tile_matrix": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -428,7 +430,7 @@ class Ops:
     def _can_fold(self, rows: int, dtype, K: int) -> bool:
         return dtype == torch.bfloat16 and rows <= min(self.SKINNY_MAX_ROWS, 16) and K % 8 == 0
 
-    def _skinny(self, a, w, n_out, gate_up, out_float32, norm=None, add_to=None, act=None):
+    def _skinny(self, a, w, n_out, gate_up, out_float32, norm=None, add_to=None, act=None, unary=None):
         """The weight-streaming product for a handful of rows (see gemm_skinny.cuh).
 
         norm: (weight, eps) or (weight, eps, stats) of an RMSNorm to take of a's rows first; stats is what the product
@@ -471,6 +473,12 @@ class Ops:
             self._check(self.lib.sb_gemm_skinny_gated(_ptr(a), _ptr(src), _ptr(out), M, n_out, K, n_splits, k_per_split,
                                                       int(copy is not None), warps, float(act[0]), float(act[1]), _ptr(buf[0]),
                                                       _ptr(buf[1]), self._stream()), "gemm_skinny_gated")
+        elif unary is not None:   # (a_pos, a_neg): the two-sided activation in the epilogue of a plain product
+            if gate_up or norm is not None or add_to is not None or out_float32:
+                raise KernelError("the two-sided activation sits in the epilogue of a plain product")
+            self._check(self.lib.sb_gemm_skinny_xielu(_ptr(a), _ptr(src), _ptr(out), M, n_out, K, n_splits, k_per_split,
+                                                      int(copy is not None), warps, float(unary[0]), float(unary[1]), _ptr(buf[0]),
+                                                      _ptr(buf[1]), self._stream()), "gemm_skinny_xielu")
         elif norm is None:
             self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(src), _ptr(out), *tail), "gemm_skinny")
         else:
@@ -1175,7 +1183,11 @@ class Ops:
         return out
 
     def linear_xielu(self, h, w_up, a_pos, a_neg):
-        """xielu(h @ w_up^T)."""
+        """xielu(h @ w_up^T).  For the few rows of a decode step the activation sits in the product's epilogue, as SwiGLU
+        does in ``linear_swiglu``."""
+        M, K = h.shape
+        if h.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and K % 8 == 0 and M <= self.SKINNY_MAX_ROWS:
+            return self._skinny(h, w_up, w_up.shape[0], False, False, unary=(a_pos, a_neg))
         return self.xielu(self.linear(h, w_up), a_pos, a_neg)
 
     def qk_norm_store(self, ctx, qkv, layer_cache, n_heads, q_norm, k_norm, eps):

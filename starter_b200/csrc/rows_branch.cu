@@ -108,8 +108,7 @@ __global__ void xielu_kernel(const T* __restrict__ z, T* __restrict__ out, long 
     pdl_launch_dependents();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const float v = to_f<T>(z[i]);
-        const float r = v > 0.f ? fmaf(a_pos * v, v, 0.5f * v) : fmaf(a_neg, expm1f(v) - v, 0.5f * v);
-        out[i] = from_f<T>(r);
+        out[i] = from_f<T>(xielu_value(v, a_pos, a_neg));
     }
 }
 
