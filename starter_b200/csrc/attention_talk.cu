@@ -15,39 +15,123 @@
 // tensor-core kernel.
 #include "attention_flex.cuh"
 
-template <class T> __device__ __forceinline__ float talk_dot(const float* qs, const T* kr, int D);
-template <> __device__ __forceinline__ float talk_dot<float>(const float* qs, const float* kr, int D) {
-    float dot = 0.f;
+// The dots of up to four query heads (their rows D apart in qs) with one key row, which is read once; every head's
+// sum runs over the columns in rising order.
+template <class T> __device__ __forceinline__ void talk_dots(const float* qs, int D, int n_heads, const T* kr, float dot[4]);
+template <> __device__ __forceinline__ void talk_dots<float>(const float* qs, int D, int n_heads, const float* kr, float dot[4]) {
     if ((D & 3) == 0) {
+#pragma unroll 8
         for (int d = 0; d < D; d += 4) {
             const float4 v = *reinterpret_cast<const float4*>(kr + d);
-            dot = fmaf(qs[d], v.x, dot);
-            dot = fmaf(qs[d + 1], v.y, dot);
-            dot = fmaf(qs[d + 2], v.z, dot);
-            dot = fmaf(qs[d + 3], v.w, dot);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < n_heads) {
+                    const float4 q = *reinterpret_cast<const float4*>(qs + (size_t)j * D + d);
+                    dot[j] = fmaf(q.w, v.w, fmaf(q.z, v.z, fmaf(q.y, v.y, fmaf(q.x, v.x, dot[j]))));
+                }
         }
     } else {
-        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], kr[d], dot);
+        for (int d = 0; d < D; ++d) {
+            const float v = kr[d];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < n_heads) dot[j] = fmaf(qs[(size_t)j * D + d], v, dot[j]);
+        }
     }
-    return dot;
 }
-template <> __device__ __forceinline__ float talk_dot<__nv_bfloat16>(const float* qs, const __nv_bfloat16* kr, int D) {
-    float dot = 0.f;
+template <>
+__device__ __forceinline__ void talk_dots<__nv_bfloat16>(const float* qs, int D, int n_heads, const __nv_bfloat16* kr, float dot[4]) {
     if ((D & 7) == 0) {
+#pragma unroll 8
         for (int d = 0; d < D; d += 8) {
             const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float f[8];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(h[e]);
-                dot = fmaf(qs[d + 2 * e], f.x, dot);
-                dot = fmaf(qs[d + 2 * e + 1], f.y, dot);
+                const float2 two = __bfloat1622float2(h[e]);
+                f[2 * e] = two.x, f[2 * e + 1] = two.y;
             }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < n_heads) {
+                    const float4 qa = *reinterpret_cast<const float4*>(qs + (size_t)j * D + d);
+                    const float4 qb = *reinterpret_cast<const float4*>(qs + (size_t)j * D + d + 4);
+                    float a = dot[j];
+                    a = fmaf(qa.w, f[3], fmaf(qa.z, f[2], fmaf(qa.y, f[1], fmaf(qa.x, f[0], a))));
+                    dot[j] = fmaf(qb.w, f[7], fmaf(qb.z, f[6], fmaf(qb.y, f[5], fmaf(qb.x, f[4], a))));
+                }
         }
     } else {
-        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], __bfloat162float(kr[d]), dot);
+        for (int d = 0; d < D; ++d) {
+            const float v = __bfloat162float(kr[d]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (j < n_heads) dot[j] = fmaf(qs[(size_t)j * D + d], v, dot[j]);
+        }
     }
-    return dot;
+}
+
+// N consecutive values of a value row as floats, in one read (the address is a multiple of N values).
+template <class T, int N> __device__ __forceinline__ void talk_read(const T* src, float f[N]);
+template <> __device__ __forceinline__ void talk_read<float, 2>(const float* src, float f[2]) {
+    const float2 v = *reinterpret_cast<const float2*>(src);
+    f[0] = v.x, f[1] = v.y;
+}
+template <> __device__ __forceinline__ void talk_read<float, 4>(const float* src, float f[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(src);
+    f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+}
+template <> __device__ __forceinline__ void talk_read<__nv_bfloat16, 2>(const __nv_bfloat16* src, float f[2]) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src));
+    f[0] = v.x, f[1] = v.y;
+}
+template <> __device__ __forceinline__ void talk_read<__nv_bfloat16, 4>(const __nv_bfloat16* src, float f[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    f[0] = a.x, f[1] = a.y, f[2] = b.x, f[3] = b.y;
+}
+
+// The value sums of one turn for up to four query heads of one key/value head (bit j of ``live``: head j goes on) when
+// a lane holds N consecutive columns (V = 32 * N): a <- a * alpha, then the turn's keys in their order.  A value row is
+// read once by the warp for all the heads, eight rows in flight.
+template <class T, int N>
+__device__ __forceinline__ void talk_values(const SbFlex& p, float* acc0, const float* wgt0, const long long* toks, int kv_head,
+                                            const float alpha[4], unsigned live, int V, int lane) {
+    const T* vbase = (const T*)p.v;
+    float a[4][N];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (live >> j & 1u)
+#pragma unroll
+            for (int e = 0; e < N; ++e) a[j][e] = acc0[(size_t)j * V + lane * N + e] * alpha[j];
+    for (int t0 = 0; t0 < 32; t0 += 8) {
+        float f[8][N];
+        bool seen[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const long long kt = toks[t0 + i];
+            seen[i] = kt >= 0;
+            if (seen[i]) talk_read<T, N>(vbase + flex_value_token(p, kt, kv_head) * p.v_row + lane * N, f[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (!seen[i]) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (live >> j & 1u) {
+                    const float w = wgt0[j * 32 + t0 + i];
+#pragma unroll
+                    for (int e = 0; e < N; ++e) a[j][e] = fmaf(w, f[i][e], a[j][e]);
+                }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (live >> j & 1u)
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc0[(size_t)j * V + lane * N + e] = a[j][e];
 }
 
 // One block per row.  Shared memory: the row's queries as floats [H * D], the table [H * H], raw and mixed scores of a
@@ -57,7 +141,7 @@ template <> __device__ __forceinline__ float talk_dot<__nv_bfloat16>(const float
 // With n_splits > 1 (decoding: few rows, many keys) blockIdx.y takes a share of the row's turns and leaves, per head, its
 // unnormalised value sums, maximum and sum in ``partial`` [row][head][split][V + 2]; talking_merge_kernel divides.
 template <class T>
-__global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __restrict__ out, int n_splits, float* __restrict__ partial) {
+__global__ void __launch_bounds__(256, 2) talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __restrict__ out, int n_splits, float* __restrict__ partial) {
     extern __shared__ __align__(16) unsigned char talk_sm[];
     const int H = p.n_heads, G = p.n_kv_heads, D = p.k_dim, V = p.v_dim, per_kv = H / G;
     long long* tok_s = reinterpret_cast<long long*>(talk_sm);            // [G][32]
@@ -89,6 +173,10 @@ __global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __r
     const int kept_turns = (kept_end + 31) / 32, turns = kept_turns + (pos + 1 - lo + 31) / 32;
     const int per_split = (turns + n_splits - 1) / n_splits;
     const int turn_lo = blockIdx.y * per_split, turn_hi = min(turns, turn_lo + per_split);
+    const int heads_per_unit = max(1, min(min(4, per_kv), H / n_warps));      // query heads that share a key row's read
+    const int head_chunks = (per_kv + heads_per_unit - 1) / heads_per_unit;
+    // columns of a value row per lane when a warp can read the row in one go (32 lanes x 2 or 4 columns), else 0
+    const int per_lane = (V == 64 || V == 128) && p.v_row % (V / 32) == 0 && (reinterpret_cast<size_t>(p.v) & 15) == 0 ? V / 32 : 0;
     {
         for (int turn = turn_lo; turn < turn_hi; ++turn) {
             const int n0 = turn < kept_turns ? turn * 32 : lo + (turn - kept_turns) * 32, end = turn < kept_turns ? kept_end : pos + 1;
@@ -96,47 +184,71 @@ __global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __r
             const bool seen = n < end;
             for (int c = warp; c < G; c += n_warps) tok_s[c * 32 + lane] = seen ? flex_token(p, slot, n, c) : -1;
             __syncthreads();
-            for (int g = warp; g < H; g += n_warps) {
-                const long long tok = tok_s[(g / per_kv) * 32 + lane];
-                float s = 0.f;
-                if (tok >= 0) {
-                    s = talk_dot<T>(qs + (size_t)g * D, kbase + tok * D, D) * p.scale;
-                    if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
-                }
-                raw[g * 32 + lane] = s;
+            // a warp takes a key/value head and up to four of its query heads (fewer when warps would idle), a lane a key
+            for (int u = warp; u < G * head_chunks; u += n_warps) {
+                const int c = u / head_chunks, g0 = c * per_kv + (u % head_chunks) * heads_per_unit;
+                const int ng = min(heads_per_unit, (c + 1) * per_kv - g0);
+                const long long tok = tok_s[c * 32 + lane];
+                float dot[4] = {0.f, 0.f, 0.f, 0.f};
+                if (tok >= 0) talk_dots<T>(qs + (size_t)g0 * D, D, ng, kbase + tok * D, dot);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (j < ng) {
+                        float s = dot[j] * p.scale;
+                        if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+                        raw[(g0 + j) * 32 + lane] = tok >= 0 ? s : 0.f;
+                    }
             }
             __syncthreads();
-            for (int h = warp; h < H; h += n_warps) {
-                const long long tok = tok_s[(h / per_kv) * 32 + lane];
-                float t;
-                if (p.talk != nullptr) {
-                    t = 0.f;
-                    for (int g = 0; g < H; ++g) t = fmaf(tb[h * H + g], raw[g * 32 + lane], t);
-                } else {
-                    t = raw[h * 32 + lane];
-                }
-                if (tok < 0) t = -INFINITY;
-                const float m_old = run_m[h];
-                const float m_new = fmaxf(m_old, warp_max(t));
-                if (m_new == -INFINITY) continue;     // nothing visible in this turn (a key without a page)
-                const float w = tok >= 0 ? expf(t - m_new) : 0.f;
-                const float alpha = expf(m_old - m_new);
-                const float sum = warp_sum(w);
-                wgt[h * 32 + lane] = w;
-                __syncwarp();
-                if (lane == 0) {
-                    run_m[h] = m_new;
-                    run_l[h] = run_l[h] * alpha + sum;
-                }
-                const long long* toks = tok_s + (h / per_kv) * 32;
-                for (int d = lane; d < V; d += 32) {
-                    float a = acc[h * V + d] * alpha;
-                    for (int t2 = 0; t2 < 32; ++t2) {
-                        const long long kt = toks[t2];
-                        if (kt >= 0) a = fmaf(wgt[h * 32 + t2], to_f<T>(vbase[flex_value_token(p, kt, h / per_kv) * p.v_row + d]), a);
+            // the same units: the heads of a unit share their key/value head's value rows
+            for (int u = warp; u < G * head_chunks; u += n_warps) {
+                const int c = u / head_chunks, g0 = c * per_kv + (u % head_chunks) * heads_per_unit;
+                const int ng = min(heads_per_unit, (c + 1) * per_kv - g0);
+                const long long tok = tok_s[c * 32 + lane];
+                float alpha[4] = {1.f, 1.f, 1.f, 1.f};
+                unsigned live = 0u;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (j >= ng) continue;
+                    const int h = g0 + j;
+                    float t;
+                    if (p.talk != nullptr) {
+                        t = 0.f;
+                        for (int g = 0; g < H; ++g) t = fmaf(tb[h * H + g], raw[g * 32 + lane], t);
+                    } else {
+                        t = raw[h * 32 + lane];
                     }
-                    acc[h * V + d] = a;
+                    if (tok < 0) t = -INFINITY;
+                    const float m_old = run_m[h];
+                    const float m_new = fmaxf(m_old, warp_max(t));
+                    if (m_new == -INFINITY) continue;     // nothing visible in this turn (a key without a page)
+                    const float w = tok >= 0 ? expf(t - m_new) : 0.f;
+                    alpha[j] = expf(m_old - m_new);
+                    const float sum = warp_sum(w);
+                    wgt[h * 32 + lane] = w;
+                    if (lane == 0) {
+                        run_m[h] = m_new;
+                        run_l[h] = run_l[h] * alpha[j] + sum;
+                    }
+                    live |= 1u << j;
                 }
+                __syncwarp();
+                const long long* toks = tok_s + c * 32;
+                if (per_lane == 2) talk_values<T, 2>(p, acc + (size_t)g0 * V, wgt + g0 * 32, toks, c, alpha, live, V, lane);
+                else if (per_lane == 4) talk_values<T, 4>(p, acc + (size_t)g0 * V, wgt + g0 * 32, toks, c, alpha, live, V, lane);
+                else
+                    for (int j = 0; j < ng; ++j) {
+                        if (!(live >> j & 1u)) continue;
+                        const int h = g0 + j;
+                        for (int d = lane; d < V; d += 32) {
+                            float a = acc[h * V + d] * alpha[j];
+                            for (int t2 = 0; t2 < 32; ++t2) {
+                                const long long kt = toks[t2];
+                                if (kt >= 0) a = fmaf(wgt[h * 32 + t2], to_f<T>(vbase[flex_value_token(p, kt, c) * p.v_row + d]), a);
+                            }
+                            acc[h * V + d] = a;
+                        }
+                    }
                 __syncwarp();
             }
             __syncthreads();
@@ -168,25 +280,32 @@ __global__ void talking_attention_general_kernel(SbFlex p, SbBatch batch, T* __r
 }
 
 // One block per (row, head): the splits' sums, scaled to their common maximum (the sink's too), added and divided.
+// Up to 64 splits: their scales are worked out once, by a thread each, and read from shared memory.
 template <class T>
 __global__ void talking_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, const float* __restrict__ sink, int n_heads,
                                      int n_splits, int V) {
+    __shared__ float scale_s[64];
+    __shared__ float red[2];
     pdl_wait();
     const long long rh = (long long)blockIdx.x * n_heads + blockIdx.y;
     const float* base = partial + rh * n_splits * (V + 2);
-    float m = sink != nullptr ? sink[blockIdx.y] : -INFINITY;
-    for (int sidx = 0; sidx < n_splits; ++sidx) m = fmaxf(m, base[(long long)sidx * (V + 2) + V]);
+    const int tid = threadIdx.x;
+    const float ms = tid < n_splits ? base[(long long)tid * (V + 2) + V] : -INFINITY;
+    float m = warp_max(ms);
+    if ((tid & 31) == 0) red[tid >> 5] = m;
+    __syncthreads();
+    m = fmaxf(red[0], red[1]);
+    if (sink != nullptr) m = fmaxf(m, sink[blockIdx.y]);
+    const float sc = ms != -INFINITY ? expf(ms - m) : 0.f;
+    scale_s[tid] = sc;
+    __syncthreads();
     float l = sink != nullptr ? expf(sink[blockIdx.y] - m) : 0.f;
-    for (int sidx = 0; sidx < n_splits; ++sidx) {
-        const float ms = base[(long long)sidx * (V + 2) + V];
-        if (ms != -INFINITY) l += base[(long long)sidx * (V + 2) + V + 1] * expf(ms - m);
-    }
-    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+    for (int sidx = 0; sidx < n_splits; ++sidx)          // in the order of the splits, the same in every thread
+        if (scale_s[sidx] != 0.f) l += base[(long long)sidx * (V + 2) + V + 1] * scale_s[sidx];
+    for (int c = tid; c < V; c += blockDim.x) {
         float o = 0.f;
-        for (int sidx = 0; sidx < n_splits; ++sidx) {
-            const float ms = base[(long long)sidx * (V + 2) + V];
-            if (ms != -INFINITY) o = fmaf(base[(long long)sidx * (V + 2) + c], expf(ms - m), o);
-        }
+        for (int sidx = 0; sidx < n_splits; ++sidx)
+            if (scale_s[sidx] != 0.f) o = fmaf(base[(long long)sidx * (V + 2) + c], scale_s[sidx], o);
         out[rh * V + c] = from_f<T>(o / l);
     }
 }
@@ -259,7 +378,7 @@ long long sb_talking_attention_general_smem(int n_heads, int n_kv_heads, int k_d
 
 int sb_talking_attention_general(int dtype, SbFlex p, SbBatch batch, void* out, int n_splits, float* partial, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
-    if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partial == nullptr)) return (int)cudaErrorInvalidValue;
+    if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && partial == nullptr)) return (int)cudaErrorInvalidValue;
     if (p.n_heads < 1 || p.n_kv_heads < 1 || p.n_heads % p.n_kv_heads || (p.v_heads > 0 && p.v_heads != p.n_kv_heads))
         return (int)cudaErrorInvalidValue;
     const long long smem = sb_talking_attention_general_smem(p.n_heads, p.n_kv_heads, p.k_dim, p.v_dim);

@@ -411,7 +411,7 @@ long long sb_talking_attention_mma_smem(int n_heads, int n_kv_heads, int k_dim, 
 int sb_talking_attention_mma(SbFlex p, SbBatch batch, void* out, int max_q_len, int n_splits, float* partial, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     if (p.v_heads > 0 && p.v_heads != p.n_kv_heads) return (int)cudaErrorInvalidValue;
-    if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partial == nullptr)) return (int)cudaErrorInvalidValue;
+    if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && partial == nullptr)) return (int)cudaErrorInvalidValue;
     int HPW, TK;
     talk_mma_shape(p.n_heads, p.n_kv_heads, p.k_dim, p.v_dim, HPW, TK);
     const int threads = p.n_heads > 8 * HPW ? 512 : 256;

@@ -31,7 +31,7 @@ __global__ void embed_sinusoid_kernel(const int* __restrict__ tokens, const T* _
     }
 }
 
-// One thread per (row, column).  Input t - taps + 1 + j of the row's sequence is a row of this step when it is not
+// A block per row (blockIdx.y shares out the columns when rows are few).  Input t - taps + 1 + j of the row's sequence is a row of this step when it is not
 // before the step's first row, else entry taps - 1 + (that index) of the sequence's record [taps - 1][width].
 // weight null: the rows are only rounded to O.
 template <class O>
@@ -47,7 +47,7 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, const float* __r
         t = row - first;
         if (state != nullptr) rec = state + (long long)batch.seq_slot[s] * state_slot;
     }
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
         float a = x[(long long)row * width + c];
         if (weight != nullptr) {
             const float* w = weight + (long long)c * taps;
@@ -72,27 +72,64 @@ __global__ void causal_conv_state_kernel(const float* __restrict__ x, float* __r
     const int s = blockIdx.x;
     const int first = batch.cu_q[s], n = batch.cu_q[s + 1] - first, keep = taps - 1;
     float* rec = state + (long long)batch.seq_slot[s] * state_slot;
-    for (int c = threadIdx.x; c < width; c += blockDim.x)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x)
         for (int e = 0; e < keep; ++e) {
             const int src = n - keep + e;     // index among the step's rows
             rec[(long long)e * width + c] = src >= 0 ? x[(long long)(first + src) * width + c] : rec[(long long)(e + n) * width + c];
         }
 }
 
-// One block per row: x += y * rstd(y) * w (* s); rounded (when given) receives the new x in the run's dtype.
-template <class T>
+// Four consecutive values of a branch's output as floats, and four floats out in the run's dtype, in one access each.
+__device__ __forceinline__ float4 read_four(const float* src) { return *reinterpret_cast<const float4*>(src); }
+__device__ __forceinline__ float4 read_four(const __nv_bfloat16* src) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void write_four(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void write_four(__nv_bfloat16* dst, float4 v) {
+    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(v.x, v.y), __floats2bfloat162_rn(v.z, v.w)};
+    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(h);
+}
+
+// One block per row: x += y * rstd(y) * w (* s); rounded (when given) receives the new x in the run's dtype.  VEC: the
+// width is a multiple of 4 and every pointer of 16 bytes: a thread takes four columns at a time.
+template <class T, bool VEC>
 __global__ void branch_norm_add_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ w,
                                        const float* __restrict__ s, T* __restrict__ rounded, int width, float eps) {
     __shared__ float red[33];
     pdl_wait();
     const long long base = (long long)blockIdx.x * width;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float v = to_f<T>(y[base + c]);
-        ss = fmaf(v, v, ss);
+    if (VEC) {
+        for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+            const float4 v = read_four(y + base + c);
+            ss = fmaf(v.w, v.w, fmaf(v.z, v.z, fmaf(v.y, v.y, fmaf(v.x, v.x, ss))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            const float v = to_f<T>(y[base + c]);
+            ss = fmaf(v, v, ss);
+        }
     }
     const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
     pdl_launch_dependents();
+    if (VEC) {
+        for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+            const float4 v = read_four(y + base + c), g = read_four(w + c), old = read_four(x + base + c);
+            float4 n = make_float4(__fmul_rn(__fmul_rn(v.x, rstd), g.x), __fmul_rn(__fmul_rn(v.y, rstd), g.y),
+                                   __fmul_rn(__fmul_rn(v.z, rstd), g.z), __fmul_rn(__fmul_rn(v.w, rstd), g.w));
+            if (s != nullptr) {
+                const float4 ls = read_four(s + c);
+                n = make_float4(__fmul_rn(n.x, ls.x), __fmul_rn(n.y, ls.y), __fmul_rn(n.z, ls.z), __fmul_rn(n.w, ls.w));
+            }
+            const float4 sum = make_float4(old.x + n.x, old.y + n.y, old.z + n.z, old.w + n.w);
+            write_four(x + base + c, sum);
+            if (rounded != nullptr) write_four(rounded + base + c, sum);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float n = __fmul_rn(__fmul_rn(to_f<T>(y[base + c]), rstd), w[c]);
         if (s != nullptr) n = __fmul_rn(n, s[c]);
@@ -132,26 +169,37 @@ int sb_causal_conv(int out_dtype, const float* x, const float* weight, float* st
     if (batch.n_rows <= 0) return 0;
     if (weight != nullptr && (taps < 1 || (taps > 1 && state == nullptr))) return (int)cudaErrorInvalidValue;
     const int threads = width >= 1024 ? 256 : 128;
+    // few rows (decoding): a row's columns go to several blocks, so that no thread walks a chain of dependent reads
+    const int shares = batch.n_rows < 64 ? (width + threads - 1) / threads : 1;
     if (out_dtype == SB_F32)
-        sb_launch(causal_conv_kernel<float>, batch.n_rows, threads, 0, stream, x, weight, (const float*)state, state_slot, batch, width,
-                  taps, (float*)out);
+        sb_launch(causal_conv_kernel<float>, dim3(batch.n_rows, shares), threads, 0, stream, x, weight, (const float*)state, state_slot,
+                  batch, width, taps, (float*)out);
     else
-        sb_launch(causal_conv_kernel<__nv_bfloat16>, batch.n_rows, threads, 0, stream, x, weight, (const float*)state, state_slot, batch,
-                  width, taps, (__nv_bfloat16*)out);
+        sb_launch(causal_conv_kernel<__nv_bfloat16>, dim3(batch.n_rows, shares), threads, 0, stream, x, weight, (const float*)state,
+                  state_slot, batch, width, taps, (__nv_bfloat16*)out);
     if (weight != nullptr && taps > 1)
-        sb_launch(causal_conv_state_kernel, batch.n_seqs, threads, 0, stream, x, state, state_slot, batch, width, taps);
+        sb_launch(causal_conv_state_kernel, dim3(batch.n_seqs, batch.n_seqs < 64 ? (width + threads - 1) / threads : 1), threads, 0,
+                  stream, x, state, state_slot, batch, width, taps);
     SB_LAUNCH_CHECK();
 }
 
 int sb_branch_norm_add(int dtype, float* x, const void* y, const float* w, const float* s, void* rounded, int rows, int width, float eps,
                        cudaStream_t stream) {
     if (rows <= 0) return 0;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    if (dtype == SB_F32)
-        sb_launch(branch_norm_add_kernel<float>, rows, threads, 0, stream, x, (const float*)y, w, s, (float*)rounded, width, eps);
-    else
-        sb_launch(branch_norm_add_kernel<__nv_bfloat16>, rows, threads, 0, stream, x, (const __nv_bfloat16*)y, w, s,
-                  (__nv_bfloat16*)rounded, width, eps);
+    auto aligned = [](const void* ptr) { return ptr == nullptr || (reinterpret_cast<size_t>(ptr) & 15) == 0; };
+    const bool vec = width % 4 == 0 && aligned(x) && aligned(y) && aligned(w) && aligned(s) && aligned(rounded);
+    const int cols = vec ? width / 4 : width;
+    const int threads = cols >= 2048 ? 512 : (cols >= 192 ? 256 : (cols >= 96 ? 128 : 64));
+#define SB_BRANCH(T, V) \
+    sb_launch(branch_norm_add_kernel<T, V>, rows, threads, 0, stream, x, (const T*)y, w, s, (T*)rounded, width, eps)
+    if (dtype == SB_F32) {
+        if (vec) SB_BRANCH(float, true);
+        else SB_BRANCH(float, false);
+    } else {
+        if (vec) SB_BRANCH(__nv_bfloat16, true);
+        else SB_BRANCH(__nv_bfloat16, false);
+    }
+#undef SB_BRANCH
     SB_LAUNCH_CHECK();
 }
 
