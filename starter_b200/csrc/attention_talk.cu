@@ -319,46 +319,55 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
     __shared__ float red[33];
     pdl_wait();
     const int row = blockIdx.x;
+    // gridDim.y == 3 (few rows): block y takes the queries, the keys or the values of the row; else one block takes all
+    const bool do_q = gridDim.y == 1 || blockIdx.y == 0, do_k = gridDim.y == 1 || blockIdx.y == 1, do_v = gridDim.y == 1 || blockIdx.y == 2;
     const int nq = n_heads * p.k_dim, nk = p.n_kv_heads * p.k_dim, nv = p.n_kv_heads * p.v_dim;
     int slot, pos;
     row_place(batch, row, slot, pos);
     const T* r = qkv + (long long)row * (nq + nk + nv);
-    float q_rstd = 1.f, k_rstd = 1.f;
-    if (q_norm != nullptr) {
-        float ss = 0.f;
+    if (do_q) {
+        float q_rstd = 1.f;
+        if (q_norm != nullptr) {
+            float ss = 0.f;
+            for (int c = threadIdx.x; c < nq; c += blockDim.x) {
+                const float x = to_f<T>(r[c]);
+                ss = fmaf(x, x, ss);
+            }
+            q_rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)nq + eps);
+        }
         for (int c = threadIdx.x; c < nq; c += blockDim.x) {
             const float x = to_f<T>(r[c]);
-            ss = fmaf(x, x, ss);
+            q_out[(long long)row * nq + c] = q_norm != nullptr ? from_f<T>(__fmul_rn(__fmul_rn(x, q_rstd), q_norm[c])) : r[c];
         }
-        q_rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)nq + eps);
     }
-    if (k_norm != nullptr) {
-        float ss = 0.f;
-        for (int c = threadIdx.x; c < nk; c += blockDim.x) {
-            const float x = to_f<T>(r[nq + c]);
-            ss = fmaf(x, x, ss);
-        }
-        k_rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)nk + eps);
-    }
-    for (int c = threadIdx.x; c < nq; c += blockDim.x) {
-        const float x = to_f<T>(r[c]);
-        q_out[(long long)row * nq + c] = q_norm != nullptr ? from_f<T>(__fmul_rn(__fmul_rn(x, q_rstd), q_norm[c])) : r[c];
-    }
+    if (!do_k && !do_v) return;
     const long long tok0 = flex_token(p, slot, pos, 0);
     if (tok0 < 0) {
         if (threadIdx.x == 0) atomicOr(status, SB_STATUS_NO_PAGE);
         return;
     }
-    for (int c = threadIdx.x; c < nk; c += blockDim.x) {
-        const int g = c / p.k_dim, d = c % p.k_dim;
-        const float x = to_f<T>(r[nq + c]);
-        ((T*)p.k)[(tok0 + (long long)g * SB_PAGE) * p.k_dim + d] =
-            k_norm != nullptr ? from_f<T>(__fmul_rn(__fmul_rn(x, k_rstd), k_norm[c])) : r[nq + c];
+    if (do_k) {
+        float k_rstd = 1.f;
+        if (k_norm != nullptr) {
+            float ss = 0.f;
+            for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+                const float x = to_f<T>(r[nq + c]);
+                ss = fmaf(x, x, ss);
+            }
+            k_rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)nk + eps);
+        }
+        for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+            const int g = c / p.k_dim, d = c % p.k_dim;
+            const float x = to_f<T>(r[nq + c]);
+            ((T*)p.k)[(tok0 + (long long)g * SB_PAGE) * p.k_dim + d] =
+                k_norm != nullptr ? from_f<T>(__fmul_rn(__fmul_rn(x, k_rstd), k_norm[c])) : r[nq + c];
+        }
     }
-    for (int c = threadIdx.x; c < nv; c += blockDim.x) {
-        const int g = c / p.v_dim, d = c % p.v_dim;
-        ((T*)p.v)[(tok0 + (long long)g * SB_PAGE) * p.v_row + d] = r[nq + nk + c];
-    }
+    if (do_v)
+        for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+            const int g = c / p.v_dim, d = c % p.v_dim;
+            ((T*)p.v)[(tok0 + (long long)g * SB_PAGE) * p.v_row + d] = r[nq + nk + c];
+        }
 }
 
 void sb_talking_merge_bf16(const float* partial, void* out, const float* sink, int n_rows, int n_heads, int n_splits, int v_dim,
@@ -408,11 +417,12 @@ int sb_qk_norm_store(int dtype, const void* qkv, void* q_out, SbBatch batch, SbF
     if (batch.n_rows <= 0) return 0;
     if (p.v_heads > 0 && p.v_heads != p.n_kv_heads) return (int)cudaErrorInvalidValue;
     const int threads = n_heads * p.k_dim >= 2048 ? 256 : 128;
+    const int parts = batch.n_rows < 64 ? 3 : 1;     // few rows (decoding): a row's queries, keys and values go to a block each
     if (dtype == SB_F32)
-        sb_launch(qk_norm_store_kernel<float>, batch.n_rows, threads, 0, stream, (const float*)qkv, (float*)q_out, batch, p, n_heads,
-                  q_norm, k_norm, eps, status);
+        sb_launch(qk_norm_store_kernel<float>, dim3(batch.n_rows, parts), threads, 0, stream, (const float*)qkv, (float*)q_out, batch, p,
+                  n_heads, q_norm, k_norm, eps, status);
     else
-        sb_launch(qk_norm_store_kernel<__nv_bfloat16>, batch.n_rows, threads, 0, stream, (const __nv_bfloat16*)qkv,
+        sb_launch(qk_norm_store_kernel<__nv_bfloat16>, dim3(batch.n_rows, parts), threads, 0, stream, (const __nv_bfloat16*)qkv,
                   (__nv_bfloat16*)q_out, batch, p, n_heads, q_norm, k_norm, eps, status);
     SB_LAUNCH_CHECK();
 }
