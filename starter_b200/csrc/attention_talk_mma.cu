@@ -15,8 +15,9 @@
 //      weight meets its value as two bfloat16 numbers hi + lo, so that it keeps 16 bits.
 //
 // The next tile's keys are fetched while steps 2 and 3 run, the next values (two buffers) as well.  A tile that every row of
-// the block sees whole skips the mask.  With n_splits > 1 blockIdx.y takes a share of the block's tiles and leaves, per
-// row and head, its unnormalised value sums, maximum and sum in ``partial`` [row][head][split][V + 2]; the merge kernel
+// the block sees whole skips the mask.  With n_splits > 1 neighbouring blocks take a share each of the 16 positions'
+// tiles (the positions with the most tiles first, all their shares together) and leave, per row and head, their
+// unnormalised value sums, maximum and sum in ``partial`` [row][head][split][V + 2]; the merge kernel
 // of attention_talk.cu adds the sink and divides.
 #include "attention_flex.cuh"
 #include "mma_utils.cuh"
@@ -56,7 +57,8 @@ talking_attention_mma_kernel(SbFlex p, SbBatch batch, __nv_bfloat16* __restrict_
     float* Tt = Ss + (size_t)H * TM_ROWS * SLD;                       // [H][HMAX]: Tt[g][h] = T[h][g], zeros beyond H
 
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, g8 = lane >> 2, t4 = lane & 3;
-    const int s = blockIdx.x / tiles_per_seq, tile = tiles_per_seq - 1 - blockIdx.x % tiles_per_seq;
+    const int split = blockIdx.x % n_splits, bx = blockIdx.x / n_splits;
+    const int s = bx / tiles_per_seq, tile = tiles_per_seq - 1 - bx % tiles_per_seq;
     if (p.talk != nullptr)
         for (int e = tid; e < H * HMAX; e += blockDim.x) {
             const int g = e / HMAX, h = e % HMAX;
@@ -74,7 +76,7 @@ talking_attention_mma_kernel(SbFlex p, SbBatch batch, __nv_bfloat16* __restrict_
     const int tb_start = max(lo_blk / TK, ta_end), tb_end = pos_last / TK;
     const int n_tiles = ta_end + (tb_end - tb_start + 1);
     const int per_split = (n_tiles + n_splits - 1) / n_splits;
-    const int it_lo = blockIdx.y * per_split, it_hi = min(n_tiles, it_lo + per_split);
+    const int it_lo = split * per_split, it_hi = min(n_tiles, it_lo + per_split);
 
     {   // the queries of all heads
         const int cpr = KD / 8;
@@ -335,7 +337,7 @@ talking_attention_mma_kernel(SbFlex p, SbBatch batch, __nv_bfloat16* __restrict_
             if (!r_valid[half]) continue;
             const long long row = q0 + first + g8 + 8 * half;
             if (n_splits > 1) {
-                float* dst = partial + ((row * H + h) * n_splits + blockIdx.y) * (VD + 2);
+                float* dst = partial + ((row * H + h) * n_splits + split) * (VD + 2);
 #pragma unroll
                 for (int i = 0; i < NT; ++i)
                     *reinterpret_cast<float2*>(dst + i * 8 + 2 * t4) = make_float2(acc[hi][i][2 * half], acc[hi][i][2 * half + 1]);
@@ -393,7 +395,7 @@ static int launch_talk_mma(SbFlex p, SbBatch batch, void* out, int max_q_len, in
         allowed = smem;
     }
     const int tiles = (max_q_len + TM_ROWS - 1) / TM_ROWS, n_warps = (p.n_heads + HPW - 1) / HPW;
-    sb_launch(talking_attention_mma_kernel<VD, HPW, TK, THREADS, HMAX>, dim3((unsigned int)(batch.n_seqs * tiles), n_splits), 32 * n_warps,
+    sb_launch(talking_attention_mma_kernel<VD, HPW, TK, THREADS, HMAX>, dim3((unsigned int)(batch.n_seqs * tiles * n_splits)), 32 * n_warps,
               (size_t)smem, stream, p, batch, (__nv_bfloat16*)out, tiles, n_splits, partial);
     if (n_splits > 1) sb_talking_merge_bf16(partial, out, p.sink, batch.n_rows, p.n_heads, n_splits, VD, stream);
     SB_LAUNCH_CHECK();

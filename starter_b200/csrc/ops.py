@@ -1270,14 +1270,15 @@ class Ops:
 
     def talk_mma_splits(self, ctx, p: SbFlex, max_pages: int) -> int:
         """Blocks along the keys per 16 positions of the tensor-core kernel: one block holds an SM (its scores of all heads
-        fill the shared memory), so a step of few positions with many keys in reach is cut until there are two blocks per
-        SM, none with less than 128 keys, four at most."""
+        fill the shared memory), so a step of few positions with many keys in reach is cut until there are three blocks per
+        SM (measured at 128 blocks of positions: four shares 186 and 388 us where one takes 209 and 706), none with less
+        than 128 keys, four at most."""
         reach = max_pages * 64
         if p.window:
             reach = min(reach, p.window + p.keep_first + 16)
         reach = min(reach, ctx.kv_bound)
         blocks = ctx.n_seqs * -(-ctx.max_q_len // 16)
-        return max(1, min(-(-2 * self.sm_count() // max(1, blocks)), reach // 128, 4))
+        return max(1, min(-(-3 * self.sm_count() // max(1, blocks)), reach // 128, 4))
 
     # ---- sampling -----------------------------------------------------------------------
 
