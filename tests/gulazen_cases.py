@@ -1,6 +1,6 @@
 """Small Gulazen configurations for the tests, and the plain implementation's logits for them.
 
-The configurations differ from one another in every size and option: convolutions of 2, 4 and 5 taps and none; fewer
+The configurations differ from one another in every size and option: convolutions of 1, 2, 4 and 5 taps and none; fewer
 key/value heads than query heads, as many, and a single head; key and value widths that differ; windows of 7, 20, one
 page and more, and none; 0, 1, 3 and more kept first tokens than a window is long; caps from 2 to 50 and none; experts
 with and without a shared expert, one choice, all experts chosen; a layer without feed-forward; dense and expert layers
@@ -73,8 +73,13 @@ CASES = {
     # five taps over a short window
     "D": _model(64, 32, 1e-5, 5, [_with(_attention(2, 2, 8, 8, window=3, keep=0, softcap=4.0), _moe(2, 1, 16)),
                                   _with(_attention(2, 1, 8, 16, window=4, keep=2, softcap=6.0), None)]),
+    # one tap (the convolution keeps no state), a window of one token, a width that is no multiple of 4, 24 heads (two
+    # per warp of the tensor-core kernel), all experts chosen and none shared, a single head without a window
+    "E": _model(77, 30, 1e-5, 1, [_with(_attention(2, 2, 6, 10, window=1, keep=0, softcap=3.0), _dense(14)),
+                                  _with(_attention(24, 8, 16, 64, window=50, keep=3, softcap=20.0), _moe(3, 3, 10)),
+                                  _with(_attention(1, 1, 4, 4), None)]),
 }
-SEEDS = {"A": 25, "B": 26, "C": 27, "D": 28}
+SEEDS = {"A": 25, "B": 26, "C": 27, "D": 28, "E": 29}
 
 
 def config(name):
