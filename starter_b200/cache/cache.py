@@ -24,7 +24,8 @@ tokens visible pins the pages that hold them: logical page j < ``pinned_pages`` 
 ``table[slot, pinned_pages + (j - pinned_pages) % ring_pages]``.
 
 A layer may ask for more than one thing (a tuple of requests: keys and values for its mixer, a state record for a
-part in front of it); its view of the cache then carries the further ones as ``aux``.
+part in front of it, state records of mixers that stand side by side); its view of the cache then carries the further
+ones as a chain: ``aux`` is the second, ``aux.aux`` the third.
 """
 
 from __future__ import annotations
@@ -219,12 +220,12 @@ class Cache:
         self.layers: List[Optional[LayerCache]] = [None] * len(requests)
         by_request: Dict[object, List[int]] = {}
         requests = list(requests)
-        further: Dict[int, object] = {}   # a layer that asks for two things: the second one, by layer
+        further: Dict[int, tuple] = {}   # a layer that asks for several things: the ones after the first, by layer
         for i, req in enumerate(requests):
             if isinstance(req, tuple):
-                if len(req) != 2 or not isinstance(req[1], StateRequest):
-                    raise CacheError(f"layer {i} asks for {req!r}; beside its first request a layer may ask for one state record")
-                requests[i], further[i] = req
+                if len(req) < 2 or not all(isinstance(r, StateRequest) for r in req[1:]):
+                    raise CacheError(f"layer {i} asks for {req!r}; beside its first request a layer may ask for state records")
+                requests[i], further[i] = req[0], tuple(req[1:])
         for i, req in enumerate(requests):
             if isinstance(req, (KVRequest, StateRequest)):
                 by_request.setdefault(req, []).append(i)
@@ -236,17 +237,21 @@ class Cache:
             self.groups.append(group)
             for j, i in enumerate(layer_ids):
                 self.layers[i] = LayerCache(group, j)
-        by_further: Dict[object, List[int]] = {}
-        for i, req in further.items():
-            by_further.setdefault(req, []).append(i)
-        for req, layer_ids in by_further.items():
+        by_further: Dict[object, List[int]] = {}   # (place in the layer's tuple, request) -> layers
+        for i, reqs in further.items():
+            for place, req in enumerate(reqs):
+                by_further.setdefault((place, req), []).append(i)
+        for (place, req), layer_ids in sorted(by_further.items(), key=lambda item: item[0][0]):
             group = StateGroup(req, layer_ids, self.n_slots, dtype, device)
             self.groups.append(group)
             for j, i in enumerate(layer_ids):
                 if self.layers[i] is None:   # the first request was None: the state is all the layer has
                     self.layers[i] = LayerCache(group, j)
                 else:
-                    self.layers[i].aux = LayerCache(group, j)
+                    last = self.layers[i]
+                    while last.aux is not None:
+                        last = last.aux
+                    last.aux = LayerCache(group, j)
         for i, req in enumerate(requests):
             if isinstance(req, SharedRequest):
                 if not 0 <= req.layer < len(requests) or self.layers[req.layer] is None:

@@ -33,6 +33,7 @@ class TensorNames:
     lm_head: str
     final_norm: Dict[str, str]
     layers: List[Dict[str, Dict[str, str]]] = field(default_factory=list)
+    loop_step: str = ""   # the [times, hidden] table of a model whose layers run in passes
 
 
 class ModelConfig:

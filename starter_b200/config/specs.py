@@ -174,7 +174,9 @@ class DiffAttentionSpec:
     queries and keys hold [map 1 | map 2] of ``head_dim`` columns each, every map is a softmax attention of its own, and
     a head's output is (a1 - lambda a2) divided by its root mean square over ``v_dim`` (eps ``norm_eps``) times
     (1 - ``diff``), with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff`` from four learned vectors.  ``window``:
-    only the last ``window`` keys are visible (None: all); ``position``: a position part applied to every map."""
+    only the last ``window`` keys are visible (None: all); ``position``: a position part applied to every map;
+    ``gate``: the heads' outputs, side by side, are multiplied element by element with sigmoid(W_g h) before the
+    output projection."""
 
     hidden_size: int
     num_heads: int
@@ -186,7 +188,66 @@ class DiffAttentionSpec:
     norm_eps: float
     window: Optional[int] = None
     position: Optional[Any] = None
+    gate: bool = False
     kind: str = "diff_attention"
+
+
+@dataclass(frozen=True)
+class KeyValueAttentionSpec:
+    """Causal grouped-query attention whose values are its keys (kind "key_value_attention"): q = W_q h, k = W_k h,
+    no value projection; v = k as it stands before the key norm.  Every option is off when None / False / 0:
+
+    * ``bias``: the query, key and output projections take a bias;
+    * ``taps``: queries and keys pass a short causal convolution over time per channel, right after the projection,
+      y_t = sum_j w[:, j] u_(t - taps + 1 + j) (not added to its input); the last ``taps`` - 1 projections are state;
+    * ``qk_norm_eps``: per head, queries and keys are divided by their root mean square and multiplied by a weight of
+      ``head_dim`` values that all heads share;
+    * ``temp_coef``, ``temp_every``: the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1);
+    * ``unit_sink``: the softmax's denominator holds one more term exp(0), with no key or value;
+    * ``head_gate``: head h's output is multiplied by sigmoid(W_g h)_h, one number per head."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    scale: float
+    bias: bool = False
+    taps: int = 0
+    qk_norm_eps: Optional[float] = None
+    temp_coef: float = 0.0
+    temp_every: int = 0
+    unit_sink: bool = False
+    head_gate: bool = False
+    kind: str = "key_value_attention"
+
+
+@dataclass(frozen=True)
+class MLSTMSpec:
+    """The matrix memory of an mLSTM layer (kind "mlstm"): per head a [head_dim, v_dim] state S and a normaliser n with a
+    running maximum m (all zero at a sequence's start).  q = W_q h / sqrt(head_dim), k = W_k h, v = W_v h; per head a log
+    input gate i = cap tanh((W_i h + b_i) / cap) and a log forget gate f = logsigmoid(cap tanh((W_f h + b_f) / cap));
+    m_t = max(f + m_(t-1), i); S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T, n_t likewise with k alone;
+    o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6); each head's o is divided by its root mean square (``norm_eps``),
+    multiplied by a weight over all heads' columns and by sigmoid(W_g h), then projected."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_dim: int
+    gate_cap: float
+    norm_eps: float
+    kind: str = "mlstm"
+
+
+@dataclass(frozen=True)
+class PairMixerSpec:
+    """Two mixers side by side that read the same input (kind "pair"): left_scale * left(h) + right_scale * right(h)."""
+
+    left: Any
+    right: Any
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "pair"
 
 
 @dataclass(frozen=True)
@@ -264,7 +325,7 @@ class GatedMLPSpec:
 class ActMLPSpec:
     """Dense feed-forward without a gate (kind "act_mlp"): down(act(up(x))).  ``activation`` "xielu": with two learned
     numbers p, q (stored with the layer), act(z) = softplus(p) z^2 + z / 2 for z > 0 and
-    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise."""
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise.  "relu2": act(z) = max(z, 0)^2, no learned numbers."""
 
     hidden_size: int
     intermediate_size: int
@@ -350,6 +411,32 @@ class PostNormBlockSpec:
 
 
 @dataclass(frozen=True)
+class SandwichBlockSpec:
+    """One layer whose branches are normed on the way in and on the way back (kind "sandwich"):
+    x += N1b(mixer(N1(x))); x += N2b(ff(N2(x))).  The inner norms are of a kind that reads the residual
+    ("grouped_rmsnorm"), the outer ones of a kind that adds to it ("branch_rmsnorm"); ``ff`` may be absent."""
+
+    mixer_norm: Any
+    mixer: Any
+    mixer_out_norm: Any
+    ff_norm: Any = None
+    ff: Any = None
+    ff_out_norm: Any = None
+    kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
+class LoopSpec:
+    """Layers ``start`` .. ``stop`` - 1 run ``times`` times in a row with the same weights, each pass with a cache of its
+    own; the rest follow.  Before each pass but the first the embedding output is added to the residual; before every
+    pass, after that, row t of a learned [times, hidden] table (t the number of the pass)."""
+
+    start: int
+    stop: int
+    times: int
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: x += mixer(norm(x)); x += ff(norm(x)) for kind "prenorm"."""
 
@@ -390,6 +477,8 @@ class ModelSpec:
 
     ``position_embedding``: a position part that enters at the embedding (its ``embed`` makes the first residual
     from the token ids and the rows' positions); None: positions enter in the mixers only.
+
+    ``loop``: a run of layers that repeats (see LoopSpec); it takes the place of ``schedule`` and needs a 32-bit residual.
     """
 
     hidden_size: int
@@ -404,6 +493,17 @@ class ModelSpec:
     residual_float32: bool = False
     streams: Optional[int] = None
     position_embedding: Optional[Any] = None
+    loop: Optional[LoopSpec] = None
 
     def execution_order(self) -> Tuple[int, ...]:
+        if self.loop is not None:
+            lo, hi, n = self.loop.start, self.loop.stop, len(self.layers)
+            return tuple(range(lo)) + tuple(range(lo, hi)) * self.loop.times + tuple(range(hi, n))
         return self.schedule if self.schedule else tuple(range(len(self.layers)))
+
+    def pass_starts(self):
+        """{place in the execution order: number of the pass that starts there} for a model with a loop."""
+        if self.loop is None:
+            return {}
+        lo, hi = self.loop.start, self.loop.stop
+        return {lo + t * (hi - lo): t for t in range(self.loop.times)}

@@ -4,7 +4,8 @@
 // Rotation ("rotate half"): of a head's first `rot` columns, column i turns with column i + rot / 2 by the angle
 // position * freqs[i]; angle, sine and cosine are 32-bit, and both are multiplied by `mag`.  Later columns pass.
 //
-// Join: with a1, a2 the two maps' results of one head, o = a1 - lam * a2, then o / sqrt(mean(o^2) + eps) * post.
+// Join: with a1, a2 the two maps' results of one head, o = a1 - lam * a2, then o / sqrt(mean(o^2) + eps) * post, and with
+// a gate (pre-activations [rows, H * V], a view of wider rows) times sigmoid(gate), element by element.
 #include "attention_flex.cuh"
 
 template <class T>
@@ -68,7 +69,7 @@ __global__ void rotate_half_store_kernel(const T* __restrict__ q, long long q_ro
 // One warp per (row, head).  a [rows, 2 H, V] holds the maps in the order (key/value head, map, head of the group).
 template <class T>
 __global__ void diff_combine_kernel(const T* __restrict__ a, T* __restrict__ out, int rows, int H, int G, int V, float lam, float eps,
-                                    float post) {
+                                    float post, const T* __restrict__ gate, long long gate_ld) {
     pdl_wait();
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -85,7 +86,13 @@ __global__ void diff_combine_kernel(const T* __restrict__ a, T* __restrict__ out
     ss = warp_sum(ss);
     const float mul = post / sqrtf(ss / (float)V + eps);
     T* o_row = out + (row * H + h) * V;
-    for (int c = lane; c < V; c += 32) o_row[c] = from_f<T>(fmaf(-lam, to_f<T>(a2[c]), to_f<T>(a1[c])) * mul);
+    if (gate == nullptr) {
+        for (int c = lane; c < V; c += 32) o_row[c] = from_f<T>(fmaf(-lam, to_f<T>(a2[c]), to_f<T>(a1[c])) * mul);
+        return;
+    }
+    const T* g_row = gate + row * gate_ld + (long long)h * V;
+    for (int c = lane; c < V; c += 32)
+        o_row[c] = from_f<T>(fmaf(-lam, to_f<T>(a2[c]), to_f<T>(a1[c])) * mul / (1.0f + expf(-to_f<T>(g_row[c]))));
 }
 
 extern "C" {
@@ -112,17 +119,18 @@ int sb_rotate_half_store(int dtype, const void* q, long long q_row, const void* 
 }
 
 int sb_diff_combine(int dtype, const void* a, void* out, int rows, int H, int G, int V, float lam, float eps, float post,
-                    cudaStream_t stream) {
+                    const void* gate, long long gate_ld, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (H < 1 || G < 1 || H % G) return (int)cudaErrorInvalidValue;
     const long long warps = (long long)rows * H;
     const int threads = 128;
     const unsigned int blocks = (unsigned int)((warps * 32 + threads - 1) / threads);
     if (dtype == SB_F32)
-        sb_launch(diff_combine_kernel<float>, blocks, threads, 0, stream, (const float*)a, (float*)out, rows, H, G, V, lam, eps, post);
+        sb_launch(diff_combine_kernel<float>, blocks, threads, 0, stream, (const float*)a, (float*)out, rows, H, G, V, lam, eps, post,
+                  (const float*)gate, gate_ld);
     else
         sb_launch(diff_combine_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)a, (__nv_bfloat16*)out, rows, H,
-                  G, V, lam, eps, post);
+                  G, V, lam, eps, post, (const __nv_bfloat16*)gate, gate_ld);
     SB_LAUNCH_CHECK();
 }
 

@@ -58,6 +58,13 @@ int sb_gemm_skinny_xielu(const void* A, const void* W, void* C, int M, int n_out
                                    SbSkinnyNorm{nullptr, 0.f, nullptr, 0, a_pos, 0.f, a_neg, 1}, nullptr, partial, counters, stream);
 }
 
+// A plain product with the squared relu in the epilogue: max(z, 0)^2, z the product as it reads back from bfloat16.
+int sb_gemm_skinny_relu2(const void* A, const void* W, void* C, int M, int n_out, int K, int n_splits, int k_per_split, int tiled,
+                         int warps, float* partial, int* counters, cudaStream_t stream) {
+    return skinny_launch<false, 4>(A, W, C, M, n_out, K, n_splits, k_per_split, 0, 0, tiled, warps, 0,
+                                   SbSkinnyNorm{nullptr, 0.f, nullptr, 0, 0.f, 0.f, 0.f, 2}, nullptr, partial, counters, stream);
+}
+
 // The tile-major copy of a row-major matrix for the kernel above.  src [halves * rows, K] bfloat16 row-major; dst
 // holds halves * ceil(rows / 16) * ceil(K / 128) tiles of 16 x 128 (sb_tile_matrix_elements of them in all).
 long long sb_tile_matrix_elements(int rows, int K, int halves) {

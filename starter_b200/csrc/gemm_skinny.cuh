@@ -91,11 +91,19 @@ struct SbSkinnyNorm {
     // and u' = clamp(u, -limit, limit); 0 (what an initialiser that stops earlier leaves) the plain silu(g) * u
     float act_alpha;
     float act_limit;
-    // what the epilogue of a plain product computes when act_unary is set: the two-sided activation xielu_value(v,
-    // act_alpha, act_neg) of the product as it reads back from bfloat16
+    // what the epilogue of a plain product computes when act_unary is set, of the product as it reads back from
+    // bfloat16: 1 the two-sided activation xielu_value(v, act_alpha, act_neg), 2 the squared relu max(v, 0)^2
     float act_neg;
     int act_unary;
 };
+
+__device__ __forceinline__ float skinny_unary(float v, int kind, float a, float b) {
+    if (kind == 2) {
+        const float r = fmaxf(v, 0.f);
+        return r * r;
+    }
+    return xielu_value(v, a, b);
+}
 
 // Stores one output and returns what C now holds there.
 __device__ __forceinline__ float skinny_store(void* C, long long o, float v, int out_f32, int accumulate) {
@@ -305,7 +313,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
                     if (GATE_UP) v2 += *cluster.map_shared_rank(&red[WPG][r][m], c);
                 }
                 if (GATE_UP) v = gated_act(v, v2, norm.act_alpha, norm.act_limit);
-                else if (norm.act_unary) v = xielu_value(__bfloat162float(__float2bfloat16_rn(v)), norm.act_alpha, norm.act_neg);
+                else if (norm.act_unary) v = skinny_unary(__bfloat162float(__float2bfloat16_rn(v)), norm.act_unary, norm.act_alpha, norm.act_neg);
                 stored = skinny_store(C, (long long)m * n_out + n0 + r, v, out_f32, accumulate);
             }
             if (stats_out != nullptr) skinny_leave_stats(stats_out, stored, m < M, m, r);
@@ -340,7 +348,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         if (m < M && n0 + r < n_out) {
             float v = red[0][r][m];
             if (GATE_UP) v = gated_act(v, red[WPG][r][m], norm.act_alpha, norm.act_limit);
-            else if (norm.act_unary) v = xielu_value(__bfloat162float(__float2bfloat16_rn(v)), norm.act_alpha, norm.act_neg);
+            else if (norm.act_unary) v = skinny_unary(__bfloat162float(__float2bfloat16_rn(v)), norm.act_unary, norm.act_alpha, norm.act_neg);
             stored = skinny_store(C, (long long)m * n_out + n0 + r, v, out_f32, accumulate);
         }
         if (stats_out != nullptr) skinny_leave_stats(stats_out, stored, m < M, m, r);

@@ -132,7 +132,21 @@ class Ops:
                                c_int, c_float, c_void_p],
             "sb_rotate_half_store": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, SbBatch,
                                      SbFlex, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p],
-            "sb_diff_combine": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
+            "sb_diff_combine": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_longlong,
+                                c_void_p],
+            "sb_mlstm_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_void_p,
+                              c_void_p, c_float, c_void_p, c_float, c_float, c_float, c_void_p, c_longlong, SbBatch, c_int, c_int, c_int,
+                              c_void_p, c_longlong, c_void_p, c_void_p],
+            "sb_conv_qk_store": [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, SbBatch, SbFlex, c_int,
+                                 c_void_p, c_void_p],
+            "sb_head_gate": [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_void_p],
+            "sb_add_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+            "sb_add_bias": [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+            "sb_scaled_sum": [c_int, c_void_p, c_float, c_void_p, c_float, c_void_p, c_longlong, c_void_p],
+            "sb_relu2": [c_int, c_void_p, c_void_p, c_longlong, c_void_p],
+            "sb_gemm_skinny_relu2": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                     c_void_p],
             "sb_gla_scan": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
                             c_float, c_float, c_void_p, c_longlong, SbBatch, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_moe_route": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -473,6 +487,12 @@ class Ops:
             self._check(self.lib.sb_gemm_skinny_gated(_ptr(a), _ptr(src), _ptr(out), M, n_out, K, n_splits, k_per_split,
                                                       int(copy is not None), warps, float(act[0]), float(act[1]), _ptr(buf[0]),
                                                       _ptr(buf[1]), self._stream()), "gemm_skinny_gated")
+        elif unary == "relu2":   # the squared relu in the epilogue of a plain product
+            if gate_up or norm is not None or add_to is not None or out_float32:
+                raise KernelError("an activation sits in the epilogue of a plain product")
+            self._check(self.lib.sb_gemm_skinny_relu2(_ptr(a), _ptr(src), _ptr(out), M, n_out, K, n_splits, k_per_split,
+                                                      int(copy is not None), warps, _ptr(buf[0]), _ptr(buf[1]), self._stream()),
+                        "gemm_skinny_relu2")
         elif unary is not None:   # (a_pos, a_neg): the two-sided activation in the epilogue of a plain product
             if gate_up or norm is not None or add_to is not None or out_float32:
                 raise KernelError("the two-sided activation sits in the epilogue of a plain product")
@@ -492,6 +512,10 @@ class Ops:
         if stats_out is not None:
             add_to.stats = stats_out
         return out
+
+    def linear_bias(self, a, w, bias):
+        """a w^T + bias (32-bit, one per output column); the bias meets the product as it is stored."""
+        return self.add_bias(self.linear(a, w), bias)
 
     def linear(self, a, w, out_float32=False, norm=None, add_to=None):
         """a [M, K] times w [N, K] transposed -> [M, N] in a's dtype, or 32-bit when asked.
@@ -1009,16 +1033,149 @@ class Ops:
                                                   _ptr(ctx.status), self._stream()), "rotate_half_store")
         return out
 
-    def diff_combine(self, a, heads, kv_heads, v_dim, lam, eps, post):
+    def diff_combine(self, a, heads, kv_heads, v_dim, lam, eps, post, gate=None):
         """a [rows, 2 * heads * v_dim], the two maps of every head in the order (key/value head, map, head of the group) ->
-        [rows, heads * v_dim]: (a1 - lam * a2) / sqrt(mean(.^2) + eps) * post, head by head."""
+        [rows, heads * v_dim]: (a1 - lam * a2) / sqrt(mean(.^2) + eps) * post, head by head.  ``gate`` [rows, heads * v_dim]
+        (a view of wider rows will do): the result times sigmoid(gate), element by element."""
         rows = a.shape[0]
         if a.shape[1] != 2 * heads * v_dim or not a.is_contiguous() or heads % kv_heads:
             raise KernelError("diff_combine: two maps of v_dim columns per head")
+        if gate is not None and (tuple(gate.shape) != (rows, heads * v_dim) or gate.stride(1) != 1 or gate.dtype != a.dtype):
+            raise KernelError("diff_combine: the gate has one column per output column, in the run's dtype")
         out = torch.empty((rows, heads * v_dim), dtype=a.dtype, device=a.device)
         self._check(self.lib.sb_diff_combine(_code(a.dtype), _ptr(a), _ptr(out), rows, heads, kv_heads, v_dim, float(lam), float(eps),
-                                             float(post), self._stream()), "diff_combine")
+                                             float(post), _ptr(gate), gate.stride(0) if gate is not None else 0, self._stream()),
+                    "diff_combine")
         return out
+
+    # ---- layers in passes, mixers side by side, keys as values, the matrix memory ----------
+
+    def add_rows(self, x, rows_too=None, vector=None, out=None):
+        """x + rows_too + vector over 32-bit rows [rows, width] (either addend may be None); into ``out`` (x itself will
+        do), else into a new tensor."""
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("add_rows: contiguous 32-bit rows")
+        if rows_too is not None and (rows_too.dtype != torch.float32 or rows_too.shape != x.shape or not rows_too.is_contiguous()):
+            raise KernelError("add_rows: the rows that are added have the shape and type of the others")
+        if vector is not None and (vector.dtype != torch.float32 or vector.numel() != x.shape[1] or not vector.is_contiguous()):
+            raise KernelError("add_rows: one 32-bit number per column")
+        if out is None:
+            out = torch.empty_like(x)
+        self._check(self.lib.sb_add_rows(_ptr(x), _ptr(rows_too), _ptr(vector), _ptr(out), x.shape[0], x.shape[1], self._stream()),
+                    "add_rows")
+        return out
+
+    def add_bias(self, y, bias):
+        """y += bias (32-bit, one per column), in place; the sum is 32-bit and rounded once."""
+        if not y.is_contiguous() or bias.dtype != torch.float32 or bias.numel() != y.shape[1]:
+            raise KernelError("add_bias: contiguous rows and one 32-bit number per column")
+        self._check(self.lib.sb_add_bias(_code(y.dtype), _ptr(y), _ptr(bias), y.shape[0], y.shape[1], self._stream()), "add_bias")
+        return y
+
+    def scaled_sum(self, a, sa, b, sb):
+        """sa * a + sb * b, element by element, 32-bit and rounded once."""
+        if a.shape != b.shape or a.dtype != b.dtype or not a.is_contiguous() or not b.is_contiguous():
+            raise KernelError("scaled_sum: two contiguous tensors of one shape and type")
+        out = torch.empty_like(a)
+        self._check(self.lib.sb_scaled_sum(_code(a.dtype), _ptr(a), float(sa), _ptr(b), float(sb), _ptr(out), a.numel(), self._stream()),
+                    "scaled_sum")
+        return out
+
+    def relu2(self, z):
+        if not z.is_contiguous():
+            raise KernelError("relu2: a contiguous tensor")
+        out = torch.empty_like(z)
+        self._check(self.lib.sb_relu2(_code(z.dtype), _ptr(z), _ptr(out), z.numel(), self._stream()), "relu2")
+        return out
+
+    def linear_relu2(self, h, w_up):
+        """max(h @ w_up^T, 0)^2.  For the few rows of a decode step the activation sits in the product's epilogue."""
+        M, K = h.shape
+        if h.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and K % 8 == 0 and M <= self.SKINNY_MAX_ROWS:
+            return self._skinny(h, w_up, w_up.shape[0], False, False, unary="relu2")
+        return self.relu2(self.linear(h, w_up))
+
+    def conv_qk_store(self, ctx, q, k, layer_cache, state, n_heads, q_bias, k_bias, q_conv, k_conv, q_norm, k_norm, eps,
+                      temp_coef, temp_every):
+        """q [rows, heads * D], k [rows, kv heads * D] (views of wider rows): plus their biases, through a short causal
+        convolution per channel (``q_conv`` [heads * D, taps]; ``state`` [slots, taps - 1, (heads + kv heads) * D] holds each
+        sequence's last biased projections and is brought up to date), normed per head with the weights of D values, the
+        queries times 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1).  The normed keys go to the cache's key rows,
+        the keys before the norm to its value rows; the queries come back as [rows, heads, D].  Biases and convolutions may
+        be None; ``temp_every`` 0 leaves the queries as they are."""
+        g = layer_cache.group
+        G, D = g.request.num_kv_heads, g.request.head_dim
+        rows = q.shape[0]
+        if (tuple(q.shape) != (rows, n_heads * D) or tuple(k.shape) != (rows, G * D) or q.stride(1) != 1 or k.stride(1) != 1
+                or q.dtype != layer_cache.k.dtype or k.dtype != q.dtype or g.v_dim != D or g.v_heads != G):
+            raise KernelError("conv_qk_store: queries or keys do not fit the layer's cache (its values are as wide as its keys)")
+        taps = 0
+        if q_conv is not None:
+            taps = q_conv.shape[1]
+            if (tuple(q_conv.shape) != (n_heads * D, taps) or tuple(k_conv.shape) != (G * D, taps) or q_conv.dtype != torch.float32
+                    or k_conv.dtype != torch.float32 or not q_conv.is_contiguous() or not k_conv.is_contiguous()):
+                raise KernelError("conv_qk_store: 32-bit convolution weights [channels, taps]")
+            if taps > 1 and (state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps - 1, (n_heads + G) * D)
+                             or not state.is_contiguous()):
+                raise KernelError(f"conv_qk_store: the state is [slots, {taps - 1}, {(n_heads + G) * D}] 32-bit numbers")
+        for t, n in ((q_bias, n_heads * D), (k_bias, G * D), (q_norm, D), (k_norm, D)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+                raise KernelError("conv_qk_store: biases and norm weights are 32-bit")
+        if q_norm is None or k_norm is None:
+            raise KernelError("conv_qk_store: queries and keys are normed")
+        out = torch.empty((rows, n_heads, D), dtype=q.dtype, device=q.device)
+        p = self._flex(layer_cache)
+        self._check(self.lib.sb_conv_qk_store(_code(q.dtype), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(q_bias), _ptr(k_bias),
+                                              _ptr(q_conv), _ptr(k_conv), int(taps), _ptr(state) if taps > 1 else None,
+                                              state.stride(0) if taps > 1 else 0, _ptr(q_norm), _ptr(k_norm), float(eps),
+                                              float(temp_coef), int(temp_every), _ptr(out), self._batch(ctx), p, n_heads,
+                                              _ptr(ctx.status), self._stream()), "conv_qk_store")
+        if taps > 1:
+            self.launches += 1   # the state's kernel
+        return out
+
+    def head_gate(self, a, z, z_col, heads, scale=1.0, out=None):
+        """a [rows, heads * V] times sigmoid(z[:, z_col + head]) (z 32-bit, [rows, any]) times ``scale``; into ``out`` (a
+        view [rows, heads * V] of wider rows will do) or a new tensor."""
+        rows, width = a.shape
+        if width % heads or not a.is_contiguous() or z.dtype != torch.float32 or z.stride(1) != 1 or z_col + heads > z.shape[1]:
+            raise KernelError("head_gate: contiguous rows of whole heads and 32-bit gates")
+        if out is None:
+            out = torch.empty_like(a)
+        elif tuple(out.shape) != (rows, width) or out.stride(1) != 1 or out.dtype != a.dtype:
+            raise KernelError("head_gate: the output has the input's shape and type")
+        self._check(self.lib.sb_head_gate(_code(a.dtype), _ptr(a), _ptr(z), z.stride(0), int(z_col), _ptr(out), out.stride(0), rows,
+                                          heads, width // heads, float(scale), self._stream()), "head_gate")
+        return out
+
+    def mlstm_scan(self, ctx, q, k, v, g, z, i_col, f_col, i_bias, f_bias, cap, norm, eps, q_scale, state, heads, dim, vdim,
+                   out_scale=1.0):
+        """The matrix memory's recurrence over every sequence's rows, from and back into ``state`` [slots, heads * dim * vdim
+        + heads * dim + heads] (S, the normaliser n, the running maximum m); q, k [rows, heads * dim] and v, g [rows, heads *
+        vdim] are views of the same wider rows; z [rows, any] 32-bit holds head h's input gate at column i_col + h and its
+        forget gate at f_col + h, before bias, cap and logsigmoid.  Returns the heads' outputs divided by their
+        normaliser, unit-normed per head, times ``norm`` [heads * vdim], sigmoid(g) and ``out_scale``."""
+        rows = q.shape[0]
+        ld = q.stride(0)
+        for t, w in ((q, heads * dim), (k, heads * dim), (v, heads * vdim), (g, heads * vdim)):
+            if tuple(t.shape) != (rows, w) or t.stride(1) != 1 or t.stride(0) != ld or t.dtype != q.dtype:
+                raise KernelError("mlstm_scan: q, k, v, g are views of rows with one stride, in the run's dtype")
+        for t in (i_bias, f_bias, norm, state):
+            if t.dtype != torch.float32 or not t.is_contiguous():
+                raise KernelError("mlstm_scan: gate biases, norm weight and state are 32-bit and contiguous")
+        if (z.dtype != torch.float32 or z.stride(1) != 1 or max(i_col, f_col) + heads > z.shape[1] or z.shape[0] != rows
+                or state.shape[1] != heads * dim * vdim + heads * dim + heads or norm.numel() != heads * vdim
+                or i_bias.numel() != heads or f_bias.numel() != heads):
+            raise KernelError("mlstm_scan: sizes do not fit")
+        y = torch.empty((rows, heads * vdim), dtype=q.dtype, device=q.device)
+        raw = torch.empty((rows, heads * vdim), dtype=torch.float32, device=q.device) if vdim > 64 else None
+        self._check(self.lib.sb_mlstm_scan(_code(q.dtype), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _ptr(z), z.stride(0), int(i_col),
+                                           int(f_col), _ptr(i_bias), _ptr(f_bias), float(cap), _ptr(norm), float(eps), float(q_scale),
+                                           float(out_scale), _ptr(state), state.stride(0), self._batch(ctx), heads, dim, vdim,
+                                           _ptr(y), y.stride(0), _ptr(raw), self._stream()), "mlstm_scan")
+        if raw is not None:
+            self.launches += 1   # the norm and the gate
+        return y
 
     def gla_scan(self, ctx, q, k, v, g, z, bias, norm, eps, tau, q_scale, state, heads, dim, vdim):
         """The gated linear recurrence over every sequence's rows, from and back into ``state`` [slots, heads * dim * vdim];

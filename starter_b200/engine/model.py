@@ -49,6 +49,12 @@ class DecoderModel:
                 roles = part_class(category, sub.kind).weight_shapes(sub)
                 weights[part_name] = {role: load(block_names[part_name][role]) for role in roles}
             self.blocks.append(block_cls(block_spec, weights, runtime))
+        self.pass_starts, self.loop_steps = {}, None
+        if getattr(spec, "loop", None) is not None:
+            if not spec.residual_float32 or spec.streams is not None or self.position is not None:
+                raise ValueError("layers that run in passes need one 32-bit residual and positions that enter in the mixers")
+            self.pass_starts = spec.pass_starts()
+            self.loop_steps = checkpoint.load(names.loop_step, torch.float32, device).float().contiguous()
         self.order = spec.execution_order()
         for i in self.order:
             if not 0 <= i < len(self.blocks):
@@ -127,8 +133,27 @@ class DecoderModel:
             x = ctx.ops.embed(tokens, self.embedding, ctx.status)
         if self.spec.embedding_scale is not None:
             x = (x.float() * self.spec.embedding_scale).to(x.dtype)
+        if self.pass_starts:
+            return self._hidden_in_passes(ctx, x)
         stream = ResidualStream(x)
         for pos, i in enumerate(self.order):
+            self.blocks[i].forward(ctx, stream, ctx.cache.layers[pos])
+        return stream
+
+    def _hidden_in_passes(self, ctx: StepContext, embedded: torch.Tensor):
+        """The layers of a model with a loop: before a pass's first layer the residual takes the embedding output (every
+        pass but the first) and the pass's own vector, in 32-bit.  The layers change the residual in place, so the
+        embedding output is kept apart: the first sum is written to a new tensor."""
+        ops = ctx.ops
+        x = None if 0 in self.pass_starts else ops.add_rows(embedded)   # layers before the loop work on a copy
+        stream = ResidualStream(x)
+        for pos, i in enumerate(self.order):
+            t = self.pass_starts.get(pos)
+            if t is not None:
+                if stream.x is None:
+                    stream.x = ops.add_rows(embedded, None, self.loop_steps[t])
+                else:
+                    ops.add_rows(stream.x, embedded if t > 0 else None, self.loop_steps[t], out=stream.x)
             self.blocks[i].forward(ctx, stream, ctx.cache.layers[pos])
         return stream
 

@@ -1,3 +1,3 @@
 """Architectures.  Importing this package registers every architecture it holds."""
 
-from . import gulazen, kudazen, nazulorn, qwen3  # noqa: F401
+from . import gulazen, kudazen, nazulorn, paditar, qwen3  # noqa: F401

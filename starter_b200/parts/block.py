@@ -131,6 +131,41 @@ class PostNormBlock:
             self.ff_norm.add_to(x, self.ff.forward(ctx, rounded))
 
 
+class SandwichBlock:
+    """Kind "sandwich": every branch is normed on the way in and on the way back,
+    x += N1b(mixer(N1(x))); x += N2b(ff(N2(x))).  The residual is one 32-bit tensor, changed in place by the outer norms
+    (kind "branch_rmsnorm"); the inner norms (kind "grouped_rmsnorm") read it and hand the run's dtype to the branch."""
+
+    @staticmethod
+    def sub_parts(spec):
+        parts = (("mixer_norm", "norm", spec.mixer_norm), ("mixer", "mixer", spec.mixer), ("mixer_out_norm", "norm", spec.mixer_out_norm))
+        if spec.ff is not None:
+            parts += (("ff_norm", "norm", spec.ff_norm), ("ff", "ff", spec.ff), ("ff_out_norm", "norm", spec.ff_out_norm))
+        return parts
+
+    def __init__(self, spec, weights, runtime):
+        self.ff = self.ff_norm = self.ff_out_norm = None
+        for name, category, sub in self.sub_parts(spec):
+            setattr(self, name, build_part(category, sub, weights[name], runtime))
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def prepare(self, cache) -> None:
+        self.mixer.prepare(cache)
+        if self.ff is not None:
+            self.ff.prepare(cache)
+
+    def forward(self, ctx, stream, layer_cache) -> None:
+        x = stream.x
+        if stream.pending is not None:
+            raise RuntimeError("a layer of this kind adds its branches itself; nothing may wait on the residual")
+        self.mixer_out_norm.add_to(x, self.mixer.forward(ctx, self.mixer_norm.forward(x), layer_cache))
+        if self.ff is not None:
+            self.ff_out_norm.add_to(x, self.ff.forward(ctx, self.ff_norm.forward(x)))
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "postnorm", PostNormBlock)
 register_part("block", "parallel", ParallelBlock)

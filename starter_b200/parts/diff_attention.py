@@ -10,7 +10,8 @@ maps of a key/value head read the same value rows (``KVRequest.v_heads``).  The 
 order (key/value head, map, head of the group) when the weights are loaded, so that the 2 H maps are 2 H query heads
 of an ordinary grouped-query attention over 2 G key heads and the library's attention kernels serve them as they
 stand; a small kernel then joins each head's two results, norms and scales.  lambda is one number per layer and is
-taken once, in 32-bit, when the weights are loaded.
+taken once, in 32-bit, when the weights are loaded.  With ``gate`` the product that makes q, k and v also makes
+W_g h, and the joining kernel multiplies its result by sigmoid(W_g h), element by element.
 """
 
 from __future__ import annotations
@@ -29,6 +30,8 @@ class DiffAttention:
         H, G, D, V, h = spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.v_dim, spec.hidden_size
         shapes = {"q": (H * 2 * D, h), "k": (G * 2 * D, h), "v": (G * V, h), "o": (h, H * V)}
         shapes.update({n: (D,) for n in ("lq1", "lk1", "lq2", "lk2")})
+        if getattr(spec, "gate", False):
+            shapes["g"] = (H * V, h)
         return shapes
 
     def __init__(self, spec, weights, runtime):
@@ -42,7 +45,8 @@ class DiffAttention:
         per = H // G
         # rows of W_q from (head, map) to (key/value head, map, head of the group)
         wq = weights["q"].reshape(G, per, 2, D, -1).permute(0, 2, 1, 3, 4).reshape(H * 2 * D, -1)
-        self.w_qkv = self.ops.prepare_matrix(torch.cat([wq, weights["k"], weights["v"]], dim=0))
+        self.gate = bool(getattr(spec, "gate", False))
+        self.w_qkv = self.ops.prepare_matrix(torch.cat([wq, weights["k"], weights["v"]] + ([weights["g"]] if self.gate else []), dim=0))
         self.w_o = self.ops.prepare_matrix(weights["o"])
         f = {n: weights[n].float() for n in ("lq1", "lk1", "lq2", "lk2")}
         self.lam = (math.exp(float((f["lq1"] * f["lk1"]).sum())) - math.exp(float((f["lq2"] * f["lk2"]).sum()))
@@ -67,9 +71,12 @@ class DiffAttention:
         q = qkv[:, :nq].view(rows, 2 * H, D)
         k = qkv[:, nq:nq + nk].view(rows, 2 * G, D)
         freqs, rot, mag = (None, 0, 1.0) if self.position is None else self.position.half_rotary()
-        q = ops.rotate_half_store(ctx, q, k, qkv[:, nq + nk:], layer_cache, freqs, rot, mag)
+        q = ops.rotate_half_store(ctx, q, k, qkv[:, nq + nk:nq + nk + G * V], layer_cache, freqs, rot, mag)
         a = ops.flex_attention(ctx, q, layer_cache, self.scale, v_dim=V, window=s.window)        # [rows, 2 H * V]
-        o = ops.diff_combine(a, H, G, V, self.lam, float(s.norm_eps), 1.0 - float(s.diff))
+        if self.gate:
+            o = ops.diff_combine(a, H, G, V, self.lam, float(s.norm_eps), 1.0 - float(s.diff), gate=qkv[:, nq + nk + G * V:])
+        else:
+            o = ops.diff_combine(a, H, G, V, self.lam, float(s.norm_eps), 1.0 - float(s.diff))
         return ops.linear(o, self.w_o)
 
 

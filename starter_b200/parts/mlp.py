@@ -54,25 +54,32 @@ class GatedMLP:
 class ActMLP:
     """Kind "act_mlp": down(act(up(x))) without a gate.  "xielu": act(z) = a+ z^2 + z / 2 for z > 0 and
     a- (exp(z) - 1 - z) + z / 2 otherwise, with a+ = softplus(p) and a- = 1/2 + softplus(q) from the layer's two learned
-    numbers ``act`` = (p, q); both are taken once at load, in 32-bit."""
+    numbers ``act`` = (p, q); both are taken once at load, in 32-bit.  "relu2": act(z) = max(z, 0)^2, nothing learned."""
 
     @staticmethod
     def weight_shapes(spec):
-        return {"up": (spec.intermediate_size, spec.hidden_size), "down": (spec.hidden_size, spec.intermediate_size), "act": (2,)}
+        shapes = {"up": (spec.intermediate_size, spec.hidden_size), "down": (spec.hidden_size, spec.intermediate_size)}
+        if spec.activation == "xielu":
+            shapes["act"] = (2,)
+        return shapes
 
     def __init__(self, spec, weights, runtime):
-        if spec.activation != "xielu":
-            raise ValueError(f"activation {spec.activation!r} is not built; 'xielu' is")
+        if spec.activation not in ("xielu", "relu2"):
+            raise ValueError(f"activation {spec.activation!r} is not built; 'xielu' and 'relu2' are")
+        self.activation = spec.activation
         self.ops = runtime.ops
         self.w_up = self.ops.prepare_matrix(weights["up"])
         self.w_down = self.ops.prepare_matrix(weights["down"])
-        pq = torch.nn.functional.softplus(weights["act"].float().cpu())
-        self.a_pos, self.a_neg = float(pq[0]), 0.5 + float(pq[1])
+        if self.activation == "xielu":
+            pq = torch.nn.functional.softplus(weights["act"].float().cpu())
+            self.a_pos, self.a_neg = float(pq[0]), 0.5 + float(pq[1])
 
     def prepare(self, cache) -> None:
         pass
 
     def forward(self, ctx, h):
+        if self.activation == "relu2":
+            return self.ops.linear(self.ops.linear_relu2(h, self.w_up), self.w_down)
         return self.ops.linear(self.ops.linear_xielu(h, self.w_up, self.a_pos, self.a_neg), self.w_down)
 
 

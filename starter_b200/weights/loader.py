@@ -38,6 +38,10 @@ def expected_tensors(spec, names) -> Tuple[Dict[str, Tuple[int, ...]], Dict[str,
     norm_cls = part_class("norm", spec.final_norm.kind)
     for role, shape in norm_cls.weight_shapes(spec.final_norm).items():
         required[names.final_norm[role]] = tuple(shape)
+    if getattr(spec, "loop", None) is not None:
+        if not names.loop_step:
+            raise WeightsError("the architecture names no tensor for the passes' vectors")
+        required[names.loop_step] = (spec.loop.times, spec.hidden_size)
     if len(names.layers) != len(spec.layers):
         raise WeightsError(f"{len(names.layers)} layers are named for {len(spec.layers)} layers")
     for block_spec, block_names in zip(spec.layers, names.layers):

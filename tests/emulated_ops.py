@@ -218,12 +218,116 @@ class EmulatedOps:
         layer_cache.v[page[ok], :, off[ok]] = v.reshape(v.shape[0], group.v_heads, group.v_dim)[ok].to(layer_cache.v.dtype)
         return turn(q).to(q.dtype)
 
-    def diff_combine(self, a, heads, kv_heads, v_dim, lam, eps, post):
+    def diff_combine(self, a, heads, kv_heads, v_dim, lam, eps, post, gate=None):
         rows, per = a.shape[0], heads // kv_heads
         maps = a.float().view(rows, kv_heads, 2, per, v_dim)
         o = maps[:, :, 0] - lam * maps[:, :, 1]
-        o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * post
-        return o.reshape(rows, heads * v_dim).to(a.dtype)
+        o = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * post).reshape(rows, heads * v_dim)
+        if gate is not None:
+            o = o * torch.sigmoid(gate.float())
+        return o.to(a.dtype)
+
+    # ---- layers in passes, mixers side by side, keys as values, the matrix memory ----------
+
+    def add_rows(self, x, rows_too=None, vector=None, out=None):
+        total = x.float()
+        if rows_too is not None:
+            total = total + rows_too
+        if vector is not None:
+            total = total + vector[None, :]
+        if out is None:
+            return total.clone()
+        out.copy_(total)
+        return out
+
+    def add_bias(self, y, bias):
+        y.copy_((y.float() + bias.float()[None, :]).to(y.dtype))
+        return y
+
+    def linear_bias(self, a, w, bias):
+        return self.add_bias(self.linear(a, w), bias)
+
+    def scaled_sum(self, a, sa, b, sb):
+        return (sa * a.float() + sb * b.float()).to(a.dtype)
+
+    def relu2(self, z):
+        return (torch.relu(z.float()) ** 2).to(z.dtype)
+
+    def linear_relu2(self, h, w_up):
+        return self.relu2(self.linear(h, w_up))
+
+    def conv_qk_store(self, ctx, q, k, layer_cache, state, n_heads, q_bias, k_bias, q_conv, k_conv, q_norm, k_norm, eps,
+                      temp_coef, temp_every):
+        group = layer_cache.group
+        G, D = group.request.num_kv_heads, group.request.head_dim
+        rows = q.shape[0]
+        u = torch.cat([q.float() + (q_bias.float() if q_bias is not None else 0.0),
+                       k.float() + (k_bias.float() if k_bias is not None else 0.0)], dim=1)
+        y = u
+        if q_conv is not None:
+            w = torch.cat([q_conv.float(), k_conv.float()], dim=0)
+            taps = w.shape[1]
+            y = torch.zeros_like(u)
+            for b in range(ctx.n_seqs):
+                slot, r0, r1 = int(ctx.seq_slot[b]), int(ctx.cu_q[b]), int(ctx.cu_q[b + 1])
+                past = state[slot].float() if taps > 1 else u.new_zeros((0, u.shape[1]))
+                hist = torch.cat([past, u[r0:r1]], dim=0)
+                for j in range(taps):
+                    y[r0:r1] += w[:, j][None, :] * hist[j:j + (r1 - r0)]
+                if taps > 1:
+                    state[slot] = hist[hist.shape[0] - (taps - 1):]
+        yq, yk = y[:, :n_heads * D].reshape(rows, n_heads, D), y[:, n_heads * D:].reshape(rows, G, D)
+
+        def unit(t, w):
+            return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.float()
+
+        slots, pos = self._positions(ctx)
+        qn = unit(yq, q_norm)
+        if temp_every:
+            qn = qn * (1.0 + temp_coef * torch.log((torch.div(pos + 1, temp_every, rounding_mode="floor") + 1).float()))[:, None, None]
+        page, off = self._physical(group, slots, pos)
+        if bool((page < 0).any()):
+            ctx.status |= 2
+        ok = page >= 0
+        layer_cache.k[page[ok], :, off[ok]] = unit(yk, k_norm)[ok].to(layer_cache.k.dtype)
+        layer_cache.v[page[ok], :, off[ok]] = yk[ok].to(layer_cache.v.dtype)
+        return qn.to(q.dtype)
+
+    def head_gate(self, a, z, z_col, heads, scale=1.0, out=None):
+        rows, width = a.shape
+        gate = torch.sigmoid(z[:, z_col:z_col + heads].float())
+        res = (a.float().reshape(rows, heads, -1) * gate[:, :, None] * scale).reshape(rows, width).to(a.dtype)
+        if out is None:
+            return res
+        out.copy_(res)
+        return out
+
+    def mlstm_scan(self, ctx, q, k, v, g, z, i_col, f_col, i_bias, f_bias, cap, norm, eps, q_scale, state, heads, dim, vdim,
+                   out_scale=1.0):
+        H, D, V = heads, dim, vdim
+        rows = q.shape[0]
+        out = torch.empty(rows, H, V, dtype=torch.float32, device=q.device)
+        cu = ctx.cu_q.tolist()
+        ig = cap * torch.tanh((z[:, i_col:i_col + H].float() + i_bias.float()) / cap)
+        fg = torch.nn.functional.logsigmoid(cap * torch.tanh((z[:, f_col:f_col + H].float() + f_bias.float()) / cap))
+        qq, kk, vv = q.float().reshape(rows, H, D) * q_scale, k.float().reshape(rows, H, D), v.float().reshape(rows, H, V)
+        for b in range(ctx.n_seqs):
+            slot = int(ctx.seq_slot[b])
+            rec = state[slot]
+            S = rec[:H * D * V].reshape(H, D, V).clone()
+            n = rec[H * D * V:H * D * V + H * D].reshape(H, D).clone()
+            m = rec[H * D * V + H * D:].clone()
+            for t in range(cu[b], cu[b + 1]):
+                m_new = torch.maximum(fg[t] + m, ig[t])
+                a_, b_ = torch.exp(fg[t] + m - m_new), torch.exp(ig[t] - m_new)
+                S = a_[:, None, None] * S + (b_[:, None] * kk[t])[:, :, None] * vv[t][:, None, :]
+                n = a_[:, None] * n + b_[:, None] * kk[t]
+                m = m_new
+                den = torch.maximum((n * qq[t]).sum(-1).abs(), torch.exp(-m)) + 1e-6
+                out[t] = torch.einsum("hk,hkv->hv", qq[t], S) / den[:, None]
+            state[slot] = torch.cat([S.reshape(-1), n.reshape(-1), m])
+        o = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps)
+        return (o.reshape(rows, H * V) * norm.float() * torch.sigmoid(g.float()) * out_scale).to(q.dtype)
 
     def gla_scan(self, ctx, q, k, v, g, z, bias, norm, eps, tau, q_scale, state, heads, dim, vdim):
         H, D, V = heads, dim, vdim
