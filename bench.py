@@ -467,8 +467,32 @@ GULAZEN_SIZES = {
     "2048": (_gulazen_raw(2048, 6, dict(heads=16, kv_heads=8, dim=128, vdim=128, mask={"size": 2048, "keep_first": 4}), ff=8192,
                           experts=32, expert_ff=1024, top=4, shared_ff=4096), NAZULORN_SIZES["2048"][0]),
 }
+def _paditar_raw(width, attention, left, right, ff, vocab=32000):
+    """A Paditar configuration of four layers (side by side, two maps, side by side, two maps) whose first two run twice:
+    six layer runs."""
+    two_maps = {"type": "attention", "mixer": dict(attention, scale=attention["dim"] ** -0.5, diff=0.5,
+                                                   rot={"base": 500000.0, "dims": attention["dim"] // 2})}
+    pair = {"type": "parallel", "mixer": {"left": dict(left, vdim=left["dim"], scale=left["dim"] ** -0.5, conv=4,
+                                                       q_temp={"coef": 0.3, "every": 64}),
+                                          "right": dict(right, gate_cap=15.0), "left_scale": 1.0, "right_scale": 0.5}}
+    mlp = {"kind": "dense", "ff": ff}
+    entries = [dict(kind, mlp=mlp) for kind in (pair, two_maps, pair, two_maps)]
+    return {"architecture": "Paditar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": entries}
+
+
+# Paditar beside Nazulorn (the closest design the library has: attention with two score maps per head, a recurrence with
+# a matrix state per head, a 32-bit residual) at the same width, layer runs, vocabulary and feed-forward work per token:
+# the dense feed-forward is as wide as Nazulorn's four chosen experts and its shared expert together; the two-map
+# attention and the matrix memory have the head counts and sizes of Nazulorn's attention and gated linear attention.
+PADITAR_SIZES = {
+    "1024": (_paditar_raw(1024, dict(heads=8, kv_heads=2, dim=64, vdim=64), dict(heads=8, kv_heads=2, dim=64),
+                          dict(heads=8, dim=64, vdim=128), ff=4096), NAZULORN_SIZES["1024"][0]),
+    "2048": (_paditar_raw(2048, dict(heads=8, kv_heads=4, dim=128, vdim=128), dict(heads=8, kv_heads=4, dim=128),
+                          dict(heads=16, dim=64, vdim=128), ff=8192), NAZULORN_SIZES["2048"][0]),
+}
 FAMILIES = {"kudazen": (FAMILY_SIZES, "qwen3", "Qwen3ForCausalLM"), "nazulorn": (NAZULORN_SIZES, "kudazen", "Kudazen"),
-            "gulazen": (GULAZEN_SIZES, "nazulorn", "Nazulorn")}
+            "gulazen": (GULAZEN_SIZES, "nazulorn", "Nazulorn"), "paditar": (PADITAR_SIZES, "nazulorn", "Nazulorn")}
 
 
 class TimedOps:
@@ -493,7 +517,7 @@ class TimedOps:
     def _cost(self, name, args, kwargs, out):
         nbytes = self._nbytes(args) + self._nbytes(kwargs.values()) + self._nbytes([out])
         flops = 0.0
-        if name in ("linear", "linear_swiglu", "linear_xielu"):
+        if name in ("linear", "linear_swiglu", "linear_xielu", "linear_relu2", "linear_bias"):
             a, w = args[0], args[1]
             flops = 2.0 * a.shape[0] * w.shape[0] * w.shape[1]
         elif name == "linear_heads":
@@ -532,6 +556,14 @@ class TimedOps:
             q, heads, dim, vdim = args[1], args[12], args[13], args[14]
             flops = 6.0 * q.shape[0] * heads * dim * vdim
             nbytes = 2 * args[0].n_seqs * heads * dim * vdim * 4 + q.shape[0] * heads * (2 * dim * 2 + 3 * vdim * 2 + dim * 4)
+        elif name == "mlstm_scan":
+            q, heads, dim, vdim = args[1], args[15], args[16], args[17]
+            flops = 6.0 * q.shape[0] * heads * dim * (vdim + 1)
+            nbytes = (2 * args[0].n_seqs * heads * (dim * vdim + dim + 1) * 4 + q.shape[0] * heads * (2 * dim * 2 + 3 * vdim * 2)
+                      + q.shape[0] * heads * 8)
+        elif name == "conv_qk_store":
+            q, k = args[1], args[2]
+            nbytes = (2 * q.numel() + 3 * k.numel()) * q.element_size()     # queries in and out, keys in, normed keys and values out
         elif name == "moe_experts":
             h, chosen, w_gu, w_down = args[0], args[1], args[3], args[4]
             pairs = chosen.numel()
@@ -563,7 +595,9 @@ class TimedOps:
             if out is not None or name not in ("qk_attention",):
                 label = name
                 if name == "flex_attention":   # the two users of this call apart: values inside the key rows (latent) or pages of their own
+                    req = args[2].group.request
                     label += ("[latent]" if kwargs.get("values_in_keys") else
+                              "[keys as values]" if kwargs.get("sink") is not None and req.v_dim == req.head_dim and args[2].aux is not None else
                               "[latent, narrow form]" if kwargs.get("sink") is not None else
                               "[two maps]" if args[2].group.v_heads != args[2].group.request.num_kv_heads else "[chunked]")
                 self.records.append((label, t0, t1) + self._cost(name, args, kwargs, out))
@@ -645,9 +679,9 @@ def _family_arm(torch, raw, peaks, prefill_tokens, batch, context, steps, warmup
 
 
 def run_family(args) -> int:
-    """--family kudazen | nazulorn | gulazen: the design at a few sizes that resemble a real model's layers (random weights),
+    """--family kudazen | nazulorn | gulazen | paditar: the design at a few sizes that resemble a real model's layers (random weights),
     beside the library's closest model of the same width, feed-forward work per token, layer count and vocabulary (Kudazen
-    beside the Qwen3 decoder, Nazulorn beside Kudazen, Gulazen beside Nazulorn).  One JSON line."""
+    beside the Qwen3 decoder, Nazulorn beside Kudazen, Gulazen and Paditar beside Nazulorn).  One JSON line."""
     import torch
     peaks, peak_source = load_peaks()
     torch.cuda.set_device(0)
@@ -875,9 +909,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0)
     ap.add_argument("--skip-points", action="store_true", help="leave out the further decode points")
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--family", default="", choices=["", "kudazen", "nazulorn", "gulazen"],
+    ap.add_argument("--family", default="", choices=["", "kudazen", "nazulorn", "gulazen", "paditar"],
                     help="instead of the default workload: this model family at a few layer sizes, beside the library's closest "
-                         "model of equal size (kudazen beside the Qwen3 shape, nazulorn beside kudazen, gulazen beside nazulorn)")
+                         "model of equal size (kudazen beside the Qwen3 shape, nazulorn beside kudazen, gulazen and paditar beside "
+                         "nazulorn)")
     ap.add_argument("--sizes", default="", help="with --family: sizes to run, with commas between them (default: all)")
     args = ap.parse_args()
 

@@ -22,7 +22,8 @@
 __device__ __forceinline__ float log_sigmoid(float z) { return z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z)); }
 
 // What a tile's tokens need of the gates: a[t] = exp(f + m_prev - m), b[t] = exp(i - m), em[t] = exp(-m).  One thread
-// per token takes the gates, then one thread walks the maxima in order.  m_run holds m between tiles.
+// per token takes the gates, one thread walks the maxima in order (an addition and a maximum per token: the chain is
+// short), then one thread per token takes the exponentials.  m_run holds m between tiles.
 __device__ __forceinline__ void mlstm_gates(const float* __restrict__ z, long long z_ld, int i_col, int f_col, float bi, float bf, float cap,
                                             int t0, int nt, float* ig, float* fg, float* as, float* bs, float* em, float* m_run) {
     const int tid = threadIdx.x;
@@ -35,13 +36,18 @@ __device__ __forceinline__ void mlstm_gates(const float* __restrict__ z, long lo
     if (tid == 0) {
         float m = *m_run;
         for (int t = 0; t < nt; ++t) {
-            const float m_new = fmaxf(fg[t] + m, ig[t]);
-            as[t] = expf(fg[t] + m - m_new);
-            bs[t] = expf(ig[t] - m_new);
-            em[t] = expf(-m_new);
-            m = m_new;
+            as[t] = m;                       // the maximum before this token, until the exponentials below
+            m = fmaxf(fg[t] + m, ig[t]);
+            em[t] = m;
         }
         *m_run = m;
+    }
+    __syncthreads();
+    if (tid < nt) {
+        const float m_prev = as[tid], m_new = em[tid];
+        as[tid] = expf(fg[tid] + m_prev - m_new);
+        bs[tid] = expf(ig[tid] - m_new);
+        em[tid] = expf(-m_new);
     }
     __syncthreads();
 }

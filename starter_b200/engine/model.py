@@ -90,6 +90,7 @@ class DecoderModel:
                 part = getattr(block, name, None)
                 if part is not None:
                     yield part
+                    yield from getattr(part, "children", tuple)()   # a part made of parts (mixers side by side)
 
     # ---- cache -------------------------------------------------------------------------
 

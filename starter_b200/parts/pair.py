@@ -43,6 +43,10 @@ class PairMixer:
         self._requests = left + right
         self._right_at = len(left)
 
+    def children(self):
+        """The two sides, for whoever walks a model's parts."""
+        return (self.left, self.right)
+
     def cache_request(self):
         if not self._requests:
             return None
