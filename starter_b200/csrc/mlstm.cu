@@ -18,6 +18,7 @@
 #define ML_TB 32   // tokens staged in shared memory at a time
 #define ML_IG 8    // threads that share a column of the state
 #define ML_VB 64   // value channels per block (the block holds one more column: the normaliser)
+#define ML_PF 4    // turns of a tile's loads that a thread keeps in registers ahead of time
 
 __device__ __forceinline__ float log_sigmoid(float z) { return z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z)); }
 
@@ -66,7 +67,7 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
                   T* __restrict__ y, long long y_ld, float* __restrict__ o_raw) {
     extern __shared__ float sm[];
     float* qs = sm;                        // [ML_TB][D]
-    float* ks = qs + ML_TB * D;            // k * b
+    float* ks = qs + ML_TB * D;
     float* vs = ks + ML_TB * D;            // [ML_TB][ML_VB]
     float* os = vs + ML_TB * ML_VB;        // [ML_TB][ML_VB + 1]
     float* gs = os + ML_TB * (ML_VB + 1);  // sigmoid(g)
@@ -91,37 +92,100 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
         S[e] = 0.f;
         if (col && e < E && i0 + e < D) S[e] = is_n ? ng[i0 + e] : Sg[(long long)(i0 + e) * V + j0 + jl];
     }
+    // A thread's first ML_PF turns of a tile's loads wait in registers while the tile before is worked on, so that the
+    // loads' way to memory and back is hidden behind the recurrence; (token, column) of turn u follow from those of
+    // turn 0 by additions.
+    T rq[ML_PF], rk[ML_PF], rv[ML_PF], rg[ML_PF];
+    const int qk_dt = n_threads / D, qk_di = n_threads % D, v_dt = n_threads / nv, v_dc = n_threads % nv;
+    const int qk_t0 = tid / D, qk_i0 = tid % D, v_t0 = tid / nv, v_c0 = tid % nv;
+    auto fetch = [&](int t0, int nt) {
+        int tt = qk_t0, i = qk_i0;
+#pragma unroll
+        for (int u = 0; u < ML_PF; ++u) {
+            if (tt < nt) {
+                const long long at = (long long)(t0 + tt) * ld + head * D + i;
+                rq[u] = q[at];
+                rk[u] = k[at];
+            }
+            tt += qk_dt;
+            i += qk_di;
+            if (i >= D) {
+                i -= D;
+                ++tt;
+            }
+        }
+        tt = v_t0;
+        int c = v_c0;
+#pragma unroll
+        for (int u = 0; u < ML_PF; ++u) {
+            if (tt < nt) {
+                const long long at = (long long)(t0 + tt) * ld + head * V + j0 + c;
+                rv[u] = v[at];
+                if (o_raw == nullptr) rg[u] = g[at];
+            }
+            tt += v_dt;
+            c += v_dc;
+            if (c >= nv) {
+                c -= nv;
+                ++tt;
+            }
+        }
+    };
+    if (row0 < row1) fetch(row0, min(ML_TB, row1 - row0));
     __syncthreads();
     for (int t0 = row0; t0 < row1; t0 += ML_TB) {
         const int nt = min(ML_TB, row1 - t0);
         __syncthreads();
         mlstm_gates(z, z_ld, i_col + head, f_col + head, bi, bf, cap, t0, nt, ig_s, fg_s, as, bs, em, &m_run);
-#pragma unroll 4
-        for (int e = tid; e < nt * D; e += n_threads) {
-            const int tt = e / D, i = e - tt * D;
-            const long long at = (long long)(t0 + tt) * ld + head * D + i;
-            qs[e] = to_f<T>(q[at]) * q_scale;
-            ks[e] = to_f<T>(k[at]) * bs[tt];
-        }
-#pragma unroll 4
-        for (int e = tid; e < nt * nv; e += n_threads) {
-            const int tt = e / nv, c = e - tt * nv;
-            const long long at = (long long)(t0 + tt) * ld + head * V + j0 + c;
-            vs[tt * ML_VB + c] = to_f<T>(v[at]);
-            if (o_raw == nullptr) gs[tt * ML_VB + c] = 1.0f / (1.0f + expf(-to_f<T>(g[at])));
+        {   // what waited in registers goes to shared memory; turns beyond ML_PF (few threads, wide heads) load now
+            int e = tid;
+#pragma unroll
+            for (int u = 0; u < ML_PF; ++u, e += n_threads)
+                if (e < nt * D) {
+                    qs[e] = to_f<T>(rq[u]) * q_scale;
+                    ks[e] = to_f<T>(rk[u]);
+                }
+            for (; e < nt * D; e += n_threads) {
+                const int tt = e / D, i = e - tt * D;
+                const long long at = (long long)(t0 + tt) * ld + head * D + i;
+                qs[e] = to_f<T>(q[at]) * q_scale;
+                ks[e] = to_f<T>(k[at]);
+            }
+            int tt = v_t0, c = v_c0;
+            e = tid;
+#pragma unroll
+            for (int u = 0; u < ML_PF; ++u, e += n_threads) {
+                if (e < nt * nv) {
+                    vs[tt * ML_VB + c] = to_f<T>(rv[u]);
+                    if (o_raw == nullptr) gs[tt * ML_VB + c] = 1.0f / (1.0f + expf(-to_f<T>(rg[u])));
+                }
+                tt += v_dt;
+                c += v_dc;
+                if (c >= nv) {
+                    c -= nv;
+                    ++tt;
+                }
+            }
+            for (; e < nt * nv; e += n_threads) {
+                const int t2 = e / nv, c2 = e - t2 * nv;
+                const long long at = (long long)(t0 + t2) * ld + head * V + j0 + c2;
+                vs[t2 * ML_VB + c2] = to_f<T>(v[at]);
+                if (o_raw == nullptr) gs[t2 * ML_VB + c2] = 1.0f / (1.0f + expf(-to_f<T>(g[at])));
+            }
         }
         __syncthreads();
+        if (t0 + ML_TB < row1) fetch(t0 + ML_TB, min(ML_TB, row1 - t0 - ML_TB));
 #pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
             const float vj = is_n ? 1.0f : (col ? vs[tt * ML_VB + jl] : 0.f);
-            const float a = as[tt];
+            const float a = as[tt], bv = bs[tt] * vj;
             const float* qt = qs + tt * D + i0;
             const float* kt = ks + tt * D + i0;
             float o = 0.f;
 #pragma unroll
             for (int e = 0; e < EMAX; ++e) {
                 if (e < E && i0 + e < D) {
-                    S[e] = fmaf(a, S[e], kt[e] * vj);
+                    S[e] = fmaf(a, S[e], kt[e] * bv);
                     o = fmaf(qt[e], S[e], o);
                 }
             }

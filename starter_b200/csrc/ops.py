@@ -159,7 +159,8 @@ class Ops:
                                c_int, c_void_p],
             "sb_embed_sinusoid": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, SbBatch, c_int, c_int, c_void_p, c_void_p],
             "sb_causal_conv": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, SbBatch, c_int, c_int, c_void_p, c_void_p],
-            "sb_branch_norm_add": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+            "sb_branch_norm_add": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_float,
+                                   c_void_p, c_void_p],
             "sb_xielu": [c_int, c_void_p, c_void_p, c_longlong, c_float, c_float, c_void_p],
             "sb_talking_attention_general": [c_int, SbFlex, SbBatch, c_void_p, c_int, c_void_p, c_void_p],
             "sb_talking_attention_mma": [SbFlex, SbBatch, c_void_p, c_int, c_int, c_void_p, c_void_p],
@@ -1149,12 +1150,13 @@ class Ops:
         return out
 
     def mlstm_scan(self, ctx, q, k, v, g, z, i_col, f_col, i_bias, f_bias, cap, norm, eps, q_scale, state, heads, dim, vdim,
-                   out_scale=1.0):
+                   out_scale=1.0, out=None):
         """The matrix memory's recurrence over every sequence's rows, from and back into ``state`` [slots, heads * dim * vdim
         + heads * dim + heads] (S, the normaliser n, the running maximum m); q, k [rows, heads * dim] and v, g [rows, heads *
         vdim] are views of the same wider rows; z [rows, any] 32-bit holds head h's input gate at column i_col + h and its
         forget gate at f_col + h, before bias, cap and logsigmoid.  Returns the heads' outputs divided by their
-        normaliser, unit-normed per head, times ``norm`` [heads * vdim], sigmoid(g) and ``out_scale``."""
+        normaliser, unit-normed per head, times ``norm`` [heads * vdim], sigmoid(g) and ``out_scale``; into ``out`` when given
+        (a view [rows, heads * vdim] of wider rows)."""
         rows = q.shape[0]
         ld = q.stride(0)
         for t, w in ((q, heads * dim), (k, heads * dim), (v, heads * vdim), (g, heads * vdim)):
@@ -1167,7 +1169,12 @@ class Ops:
                 or state.shape[1] != heads * dim * vdim + heads * dim + heads or norm.numel() != heads * vdim
                 or i_bias.numel() != heads or f_bias.numel() != heads):
             raise KernelError("mlstm_scan: sizes do not fit")
-        y = torch.empty((rows, heads * vdim), dtype=q.dtype, device=q.device)
+        if out is None:
+            y = torch.empty((rows, heads * vdim), dtype=q.dtype, device=q.device)
+        elif tuple(out.shape) != (rows, heads * vdim) or out.stride(1) != 1 or out.dtype != q.dtype:
+            raise KernelError("mlstm_scan: the output has one column per head and value channel, in the run's dtype")
+        else:
+            y = out
         raw = torch.empty((rows, heads * vdim), dtype=torch.float32, device=q.device) if vdim > 64 else None
         self._check(self.lib.sb_mlstm_scan(_code(q.dtype), _ptr(q), _ptr(k), _ptr(v), _ptr(g), ld, _ptr(z), z.stride(0), int(i_col),
                                            int(f_col), _ptr(i_bias), _ptr(f_bias), float(cap), _ptr(norm), float(eps), float(q_scale),
@@ -1311,10 +1318,23 @@ class Ops:
             self.launches += 1   # the state's kernel
         return out
 
-    def branch_norm_add(self, x, y, weight, scale, eps, out_dtype):
+    def branch_norm_add(self, x, y, weight, scale, eps, out_dtype, next_norm=None):
         """x += y / sqrt(mean(y^2) + eps) * weight (* scale), in place and 32-bit; returns the new x rounded to
-        ``out_dtype`` (x itself when it has that type), or None when ``out_dtype`` is None."""
+        ``out_dtype`` (x itself when it has that type), or None when ``out_dtype`` is None.  ``next_norm`` = (weight, eps)
+        of the RMS norm that the next branch takes of the residual: the kernel then returns that norm of the new x in
+        y's type instead (one pass over the row for the sum, the norm and the rounding)."""
         rows, width = x.shape
+        if next_norm is not None:
+            next_w, next_eps = next_norm
+            if next_w.dtype != torch.float32 or next_w.numel() != width or not next_w.is_contiguous():
+                raise KernelError("branch_norm_add: the next norm's weight is 32-bit, one per column")
+            if (x.dtype != torch.float32 or tuple(y.shape) != (rows, width) or not x.is_contiguous() or not y.is_contiguous()
+                    or weight.dtype != torch.float32 or weight.numel() != width or scale is not None):
+                raise KernelError("branch_norm_add: a contiguous 32-bit residual, a branch output of its shape, 32-bit weights")
+            normed = torch.empty((rows, width), dtype=y.dtype, device=x.device)
+            self._check(self.lib.sb_branch_norm_add(_code(y.dtype), _ptr(x), _ptr(y), _ptr(weight), None, None, rows, width, float(eps),
+                                                    _ptr(next_w), float(next_eps), _ptr(normed), self._stream()), "branch_norm_add")
+            return normed
         if (x.dtype != torch.float32 or tuple(y.shape) != (rows, width) or not x.is_contiguous() or not y.is_contiguous()
                 or weight.dtype != torch.float32 or weight.numel() != width or (scale is not None and (scale.dtype != torch.float32
                                                                                                     or scale.numel() != width))):
@@ -1325,7 +1345,7 @@ class Ops:
                 raise KernelError("branch_norm_add: the rounded copy has the branch output's type")
             rounded = torch.empty((rows, width), dtype=out_dtype, device=x.device)
         self._check(self.lib.sb_branch_norm_add(_code(y.dtype), _ptr(x), _ptr(y), _ptr(weight), _ptr(scale), _ptr(rounded), rows, width,
-                                                float(eps), self._stream()), "branch_norm_add")
+                                                float(eps), None, 0.0, None, self._stream()), "branch_norm_add")
         if out_dtype is None:
             return None
         return x if rounded is None else rounded

@@ -2,7 +2,8 @@
 //
 //   embed_sinusoid   x = table[token] + position vector (column 2i: sin(pos * f_i), column 2i + 1: cos(pos * f_i))
 //   causal_conv      out_t = x_t + sum_j w[:, j] * x_(t - taps + 1 + j), inputs before the step from a state record
-//   branch_norm_add  x += y / sqrt(mean(y^2) + eps) * w * s, and the new x rounded to the run's dtype for the next reader
+//   branch_norm_add  x += y / sqrt(mean(y^2) + eps) * w * s, and the new x rounded to the run's dtype for the next reader,
+//                    or its RMS norm times a second weight when the next reader norms the residual first
 //   xielu            a+ z^2 + z / 2 for z > 0, a- (exp(z) - 1 - z) + z / 2 otherwise
 //
 // Angles, sines, the convolution's sum, the norm and the residual sum are 32-bit in every run.
@@ -94,11 +95,15 @@ __device__ __forceinline__ void write_four(__nv_bfloat16* dst, float4 v) {
 }
 
 // One block per row: x += y * rstd(y) * w (* s); rounded (when given) receives the new x in the run's dtype.  VEC: the
-// width is a multiple of 4 and every pointer of 16 bytes: a thread takes four columns at a time.
+// width is a multiple of 4 and every pointer of 16 bytes: a thread takes four columns at a time.  normed (when given)
+// receives the RMS norm of the new x times next_w: what the next branch reads when it norms the residual first; a
+// thread then reads back the columns it wrote itself.
 template <class T, bool VEC>
 __global__ void branch_norm_add_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ w,
-                                       const float* __restrict__ s, T* __restrict__ rounded, int width, float eps) {
+                                       const float* __restrict__ s, T* __restrict__ rounded, int width, float eps,
+                                       const float* __restrict__ next_w, float next_eps, T* __restrict__ normed) {
     __shared__ float red[33];
+    float ss2 = 0.f;
     pdl_wait();
     const long long base = (long long)blockIdx.x * width;
     float ss = 0.f;
@@ -127,6 +132,13 @@ __global__ void branch_norm_add_kernel(float* __restrict__ x, const T* __restric
             const float4 sum = make_float4(old.x + n.x, old.y + n.y, old.z + n.z, old.w + n.w);
             write_four(x + base + c, sum);
             if (rounded != nullptr) write_four(rounded + base + c, sum);
+            ss2 = fmaf(sum.w, sum.w, fmaf(sum.z, sum.z, fmaf(sum.y, sum.y, fmaf(sum.x, sum.x, ss2))));
+        }
+        if (normed == nullptr) return;
+        const float rstd2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)width + next_eps);
+        for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+            const float4 v = read_four(x + base + c), g = read_four(next_w + c);
+            write_four(normed + base + c, make_float4(v.x * rstd2 * g.x, v.y * rstd2 * g.y, v.z * rstd2 * g.z, v.w * rstd2 * g.w));
         }
         return;
     }
@@ -136,7 +148,11 @@ __global__ void branch_norm_add_kernel(float* __restrict__ x, const T* __restric
         const float v = x[base + c] + n;
         x[base + c] = v;
         if (rounded != nullptr) rounded[base + c] = from_f<T>(v);
+        ss2 = fmaf(v, v, ss2);
     }
+    if (normed == nullptr) return;
+    const float rstd2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)width + next_eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) normed[base + c] = from_f<T>(x[base + c] * rstd2 * next_w[c]);
 }
 
 template <class T>
@@ -184,14 +200,17 @@ int sb_causal_conv(int out_dtype, const float* x, const float* weight, float* st
 }
 
 int sb_branch_norm_add(int dtype, float* x, const void* y, const float* w, const float* s, void* rounded, int rows, int width, float eps,
-                       cudaStream_t stream) {
+                       const float* next_w, float next_eps, void* normed, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if ((next_w == nullptr) != (normed == nullptr)) return (int)cudaErrorInvalidValue;
     auto aligned = [](const void* ptr) { return ptr == nullptr || (reinterpret_cast<size_t>(ptr) & 15) == 0; };
-    const bool vec = width % 4 == 0 && aligned(x) && aligned(y) && aligned(w) && aligned(s) && aligned(rounded);
+    const bool vec = width % 4 == 0 && aligned(x) && aligned(y) && aligned(w) && aligned(s) && aligned(rounded) && aligned(next_w)
+                     && aligned(normed);
     const int cols = vec ? width / 4 : width;
     const int threads = cols >= 2048 ? 512 : (cols >= 192 ? 256 : (cols >= 96 ? 128 : 64));
 #define SB_BRANCH(T, V) \
-    sb_launch(branch_norm_add_kernel<T, V>, rows, threads, 0, stream, x, (const T*)y, w, s, (T*)rounded, width, eps)
+    sb_launch(branch_norm_add_kernel<T, V>, rows, threads, 0, stream, x, (const T*)y, w, s, (T*)rounded, width, eps, next_w, next_eps, \
+              (T*)normed)
     if (dtype == SB_F32) {
         if (vec) SB_BRANCH(float, true);
         else SB_BRANCH(float, false);

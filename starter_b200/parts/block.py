@@ -134,7 +134,8 @@ class PostNormBlock:
 class SandwichBlock:
     """Kind "sandwich": every branch is normed on the way in and on the way back,
     x += N1b(mixer(N1(x))); x += N2b(ff(N2(x))).  The residual is one 32-bit tensor, changed in place by the outer norms
-    (kind "branch_rmsnorm"); the inner norms (kind "grouped_rmsnorm") read it and hand the run's dtype to the branch."""
+    (kind "branch_rmsnorm"); the inner norms (kind "grouped_rmsnorm") read it and hand the run's dtype to the branch.  The
+    kernel that adds the mixer's normed output also norms the new residual for the feed-forward."""
 
     @staticmethod
     def sub_parts(spec):
@@ -160,9 +161,12 @@ class SandwichBlock:
         x = stream.x
         if stream.pending is not None:
             raise RuntimeError("a layer of this kind adds its branches itself; nothing may wait on the residual")
-        self.mixer_out_norm.add_to(x, self.mixer.forward(ctx, self.mixer_norm.forward(x), layer_cache))
-        if self.ff is not None:
-            self.ff_out_norm.add_to(x, self.ff.forward(ctx, self.ff_norm.forward(x)))
+        y = self.mixer.forward(ctx, self.mixer_norm.forward(x), layer_cache)
+        if self.ff is None:
+            self.mixer_out_norm.add_to(x, y)
+            return
+        h = self.mixer_out_norm.add_to(x, y, then=self.ff_norm)    # the mixer's way back and the feed-forward's way in: one kernel
+        self.ff_out_norm.add_to(x, self.ff.forward(ctx, h))
 
 
 register_part("block", "prenorm", PreNormBlock)

@@ -39,7 +39,7 @@ class KeyValueAttention:
             shapes["g"] = (H, h)
         return shapes
 
-    def __init__(self, spec, weights, runtime, out_scale: float = 1.0):
+    def __init__(self, spec, weights, runtime, out_scale: float = 1.0, own_products: bool = True):
         H, G, D = spec.num_heads, spec.num_kv_heads, spec.head_dim
         if H % G:
             raise ValueError(f"{H} query heads cannot share {G} key/value heads evenly")
@@ -53,9 +53,15 @@ class KeyValueAttention:
         def f32(name):
             return weights[name].float().contiguous()
 
-        self.w_qk = self.ops.prepare_matrix(torch.cat([weights["q"], weights["k"]], dim=0))
-        self.w_o = self.ops.prepare_matrix(weights["o"])
-        self.w_g = self.ops.prepare_matrix(weights["g"]) if spec.head_gate else None
+        # ``own_products`` False: a mixer that stands beside another one hands its matrices to the pair, which makes one
+        # product of both sides' rows (``joint``: rows of the input product, rows of the 32-bit gate product, W_o)
+        self.joint = (torch.cat([weights["q"], weights["k"]], dim=0), weights["g"] if spec.head_gate else None, weights["o"])
+        self.w_qk = self.w_o = self.w_g = None
+        if own_products:
+            self.w_qk = self.ops.prepare_matrix(self.joint[0])
+            self.w_o = self.ops.prepare_matrix(weights["o"])
+            self.w_g = self.ops.prepare_matrix(weights["g"]) if spec.head_gate else None
+            self.joint = None
         self.q_bias = f32("q_bias") if spec.bias else None
         self.k_bias = f32("k_bias") if spec.bias else None
         self.o_bias = (f32("o_bias") * self.out_scale).contiguous() if spec.bias else None
@@ -77,22 +83,25 @@ class KeyValueAttention:
     def prepare(self, cache) -> None:
         pass
 
-    def heads_output(self, ctx, h, layer_cache, out=None):
-        """The gated heads' outputs times ``out_scale``, [rows, heads * head_dim], before the output projection; into
-        ``out`` when given (a view of wider rows)."""
+    def heads_from(self, ctx, qk, z, z_col, layer_cache, out=None):
+        """From the projections qk [rows, (heads + kv heads) * head_dim] (a view of wider rows will do) and the gates'
+        32-bit pre-activations z[:, z_col : z_col + heads]: the gated heads' outputs times ``out_scale``, [rows, heads *
+        head_dim], before the output projection; into ``out`` when given (a view of wider rows)."""
         s, ops = self.spec, self.ops
-        H, G, D = s.num_heads, s.num_kv_heads, s.head_dim
-        qk = ops.linear(h, self.w_qk)
+        H, D = s.num_heads, s.head_dim
         state = layer_cache.aux.state if s.taps > 1 else None
         q = ops.conv_qk_store(ctx, qk[:, :H * D], qk[:, H * D:], layer_cache, state, H, self.q_bias, self.k_bias, self.q_conv,
                               self.k_conv, self.q_norm, self.k_norm, self.eps, float(s.temp_coef), int(s.temp_every))
         a = ops.flex_attention(ctx, q, layer_cache, float(s.scale), v_dim=D, sink=self.sink)
-        if self.w_g is None:
+        if z is None:
             if self.out_scale == 1.0 and out is None:
                 return a
             raise NotImplementedError("a share of the output without a head gate is not built")
-        z = ops.linear(h, self.w_g, out_float32=True)
-        return ops.head_gate(a, z, 0, H, self.out_scale, out=out)
+        return ops.head_gate(a, z, z_col, H, self.out_scale, out=out)
+
+    def heads_output(self, ctx, h, layer_cache):
+        z = self.ops.linear(h, self.w_g, out_float32=True) if self.w_g is not None else None
+        return self.heads_from(ctx, self.ops.linear(h, self.w_qk), z, 0, layer_cache)
 
     def forward(self, ctx, h, layer_cache):
         o = self.heads_output(ctx, h, layer_cache)

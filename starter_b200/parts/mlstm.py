@@ -31,16 +31,21 @@ class MatrixMemory:
         return {"q": (kd, h), "k": (kd, h), "v": (vd, h), "g": (vd, h), "o": (h, vd), "norm": (vd,),
                 "i": (H, h), "i_bias": (H,), "f": (H, h), "f_bias": (H,)}
 
-    def __init__(self, spec, weights, runtime, out_scale: float = 1.0):
+    def __init__(self, spec, weights, runtime, out_scale: float = 1.0, own_products: bool = True):
         if not spec.gate_cap > 0:
             raise ValueError(f"the gates' cap must be positive, got {spec.gate_cap}")
         self.spec = spec
         self.ops = runtime.ops
         self.out_scale = float(out_scale)
         self.kd, self.vd = spec.num_heads * spec.head_dim, spec.num_heads * spec.v_dim
-        self.w_in = self.ops.prepare_matrix(torch.cat([weights[n] for n in ("q", "k", "v", "g")], dim=0))
-        self.w_gates = self.ops.prepare_matrix(torch.cat([weights["i"], weights["f"]], dim=0))
-        self.w_o = self.ops.prepare_matrix(weights["o"])
+        # ``own_products`` False: the pair this mixer stands in makes one product of both sides' rows (see ``joint``)
+        self.joint = (torch.cat([weights[n] for n in ("q", "k", "v", "g")], dim=0), torch.cat([weights["i"], weights["f"]], dim=0),
+                      weights["o"])
+        self.w_in = self.w_gates = self.w_o = None
+        if own_products:
+            self.w_in, self.w_gates, self.w_o = (self.ops.prepare_matrix(w) for w in self.joint)
+            self.joint = None
+        self.o_bias = None
         self.i_bias = weights["i_bias"].float().contiguous()
         self.f_bias = weights["f_bias"].float().contiguous()
         self.norm = weights["norm"].float().contiguous()
@@ -52,15 +57,18 @@ class MatrixMemory:
     def prepare(self, cache) -> None:
         pass
 
+    def heads_from(self, ctx, p, z, z_col, layer_cache, out=None):
+        """From the projections p [rows, q | k | v | g] (a view of wider rows will do) and the gates' 32-bit
+        pre-activations z[:, z_col : z_col + 2 heads] (input gates, then forget gates): what the output projection reads,
+        times ``out_scale``, [rows, heads * v_dim]; into ``out`` when given (a view of wider rows)."""
+        s, kd, vd = self.spec, self.kd, self.vd
+        return self.ops.mlstm_scan(ctx, p[:, :kd], p[:, kd:2 * kd], p[:, 2 * kd:2 * kd + vd], p[:, 2 * kd + vd:2 * kd + 2 * vd], z, z_col,
+                                   z_col + s.num_heads, self.i_bias, self.f_bias, float(s.gate_cap), self.norm, float(s.norm_eps),
+                                   float(s.head_dim) ** -0.5, layer_cache.state, s.num_heads, s.head_dim, s.v_dim,
+                                   out_scale=self.out_scale, out=out)
+
     def heads_output(self, ctx, h, layer_cache):
-        """What the output projection reads, times ``out_scale``: [rows, heads * v_dim]."""
-        s, ops, kd, vd = self.spec, self.ops, self.kd, self.vd
-        p = ops.linear(h, self.w_in)
-        z = ops.linear(h, self.w_gates, out_float32=True)
-        return ops.mlstm_scan(ctx, p[:, :kd], p[:, kd:2 * kd], p[:, 2 * kd:2 * kd + vd], p[:, 2 * kd + vd:], z, 0, s.num_heads,
-                              self.i_bias, self.f_bias, float(s.gate_cap), self.norm, float(s.norm_eps),
-                              float(s.head_dim) ** -0.5, layer_cache.state, s.num_heads, s.head_dim, s.v_dim,
-                              out_scale=self.out_scale)
+        return self.heads_from(ctx, self.ops.linear(h, self.w_in), self.ops.linear(h, self.w_gates, out_float32=True), 0, layer_cache)
 
     def forward(self, ctx, h, layer_cache):
         return self.ops.linear(self.heads_output(ctx, h, layer_cache), self.w_o)

@@ -84,8 +84,15 @@ class BranchRMSNorm:
         self.ops = runtime.ops
         self.dtype = runtime.dtype
 
-    def add_to(self, x, y, want_rounded: bool = False):
-        """x += norm(y) (* scale); returns the new x in the run's dtype when ``want_rounded`` (x itself if it has that type)."""
+    def add_to(self, x, y, want_rounded: bool = False, then=None):
+        """x += norm(y) (* scale); returns the new x in the run's dtype when ``want_rounded`` (x itself if it has that type).
+        ``then``: the norm that the next branch takes of the residual (kind "grouped_rmsnorm", one group); its result
+        for the new x is returned instead, from the same kernel."""
+        if then is not None:
+            if self.scale is None and getattr(then, "groups", 0) == 1 and then.weight.dtype == x.dtype:
+                return self.ops.branch_norm_add(x, y, self.weight, None, self.eps, self.dtype, next_norm=(then.weight, then.eps))
+            self.ops.branch_norm_add(x, y, self.weight, self.scale, self.eps, None)
+            return then.forward(x)
         return self.ops.branch_norm_add(x, y, self.weight, self.scale, self.eps, self.dtype if want_rounded else None)
 
 

@@ -303,7 +303,8 @@ class EmulatedOps:
         return out
 
     def mlstm_scan(self, ctx, q, k, v, g, z, i_col, f_col, i_bias, f_bias, cap, norm, eps, q_scale, state, heads, dim, vdim,
-                   out_scale=1.0):
+                   out_scale=1.0, out=None):
+        dest = out
         H, D, V = heads, dim, vdim
         rows = q.shape[0]
         out = torch.empty(rows, H, V, dtype=torch.float32, device=q.device)
@@ -327,7 +328,11 @@ class EmulatedOps:
                 out[t] = torch.einsum("hk,hkv->hv", qq[t], S) / den[:, None]
             state[slot] = torch.cat([S.reshape(-1), n.reshape(-1), m])
         o = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps)
-        return (o.reshape(rows, H * V) * norm.float() * torch.sigmoid(g.float()) * out_scale).to(q.dtype)
+        res = (o.reshape(rows, H * V) * norm.float() * torch.sigmoid(g.float()) * out_scale).to(q.dtype)
+        if dest is None:
+            return res
+        dest.copy_(res)
+        return dest
 
     def gla_scan(self, ctx, q, k, v, g, z, bias, norm, eps, tau, q_scale, state, heads, dim, vdim):
         H, D, V = heads, dim, vdim
@@ -494,12 +499,14 @@ class EmulatedOps:
             out[r] = (torch.einsum("hn,nhd->hd", e, vv) / total).reshape(-1).to(dt)
         return out
 
-    def branch_norm_add(self, x, y, weight, scale, eps, out_dtype):
+    def branch_norm_add(self, x, y, weight, scale, eps, out_dtype, next_norm=None):
         yf = y.float()
         n = yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * weight.float()
         if scale is not None:
             n = n * scale.float()
         x.add_(n)
+        if next_norm is not None:
+            return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + next_norm[1]) * next_norm[0].float()).to(y.dtype)
         if out_dtype is None:
             return None
         return x if x.dtype == out_dtype else x.to(out_dtype)
