@@ -16,9 +16,12 @@
 #include "common.cuh"
 
 #define ML_TB 32   // tokens staged in shared memory at a time
-#define ML_IG 8    // threads that share a column of the state
+#define ML_IG 8    // threads that share a column group of the state
+#define ML_CG 2    // neighbouring columns that a thread holds
 #define ML_VB 64   // value channels per block (the block holds one more column: the normaliser)
-#define ML_PF 4    // turns of a tile's loads that a thread keeps in registers ahead of time
+#define ML_VW (ML_VB + ML_CG)                          // columns of a staged row of values: 16-byte rows with the normaliser's column
+#define ML_THREADS (((ML_VB / ML_CG + 1) * ML_IG + 31) / 32 * 32)  // a column group per 8 threads, rounded up to whole warps
+#define ML_PF 8    // turns of a tile's loads that a thread keeps in registers ahead of time
 
 __device__ __forceinline__ float log_sigmoid(float z) { return z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z)); }
 
@@ -53,31 +56,35 @@ __device__ __forceinline__ void mlstm_gates(const float* __restrict__ z, long lo
     __syncthreads();
 }
 
-// One block per (sequence, head, group of ML_VB value channels), 8 threads per column.  Thread (jl, ig) owns, in
-// registers, the entries S[i][j] of its column for E = ceil(D / 8) key channels; column nv of the block is the
-// normaliser.  The eight threads of a column are neighbouring lanes and add their shares with three shuffles.  With
-// o_raw the head's columns are shared out over several blocks, which leave h_t there for mlstm_finish_kernel; without,
-// one block holds the whole head and finishes it itself.
-template <class T, int EMAX>
-__global__ void __launch_bounds__((ML_VB + 4) * ML_IG)
+// One block per (sequence, head, group of ML_VB value channels).  A thread owns, in registers, the entries S[i][j] of
+// ML_CG neighbouring columns j for E = ceil(D / 8) key channels i: what it reads of q_t and k_t from shared memory
+// serves ML_CG columns.  Column nv of
+// the block is the normaliser (its "value" is 1).  The eight threads of a column group are neighbouring lanes and add
+// their shares with three shuffles per column.  EXACT: D = 8 * EMAX with EMAX a multiple of 4; a thread's key channels
+// are then dealt out four at a time, ((e / 4) * 8 + ig) * 4 + e % 4, so that the eight lanes read 128 consecutive
+// bytes, 16 a lane.  With o_raw the head's columns are shared out over several blocks, which leave h_t there for
+// mlstm_finish_kernel; without, one block holds the whole head and finishes it itself.
+template <class T, int EMAX, bool EXACT>
+__global__ void __launch_bounds__(ML_THREADS)
 mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g, long long ld,
                   const float* __restrict__ z, long long z_ld, int i_col, int f_col, const float* __restrict__ i_bias,
                   const float* __restrict__ f_bias, float cap, const float* __restrict__ norm_w, float eps, float q_scale,
                   float out_scale, float* __restrict__ state, long long state_stride, SbBatch batch, int H, int D, int V,
                   T* __restrict__ y, long long y_ld, float* __restrict__ o_raw) {
-    extern __shared__ float sm[];
-    float* qs = sm;                        // [ML_TB][D]
+    extern __shared__ float4 sm4[];
+    float* qs = reinterpret_cast<float*>(sm4);   // [ML_TB][D]
     float* ks = qs + ML_TB * D;
-    float* vs = ks + ML_TB * D;            // [ML_TB][ML_VB]
-    float* os = vs + ML_TB * ML_VB;        // [ML_TB][ML_VB + 1]
-    float* gs = os + ML_TB * (ML_VB + 1);  // sigmoid(g)
+    float* vs = ks + ML_TB * D;                  // [ML_TB][ML_VW]: the values, 1 in column nv, 0 beyond
+    float* os = vs + ML_TB * ML_VW;              // [ML_TB][ML_VW]
+    float* gs = os + ML_TB * ML_VW;              // [ML_TB][ML_VB]: sigmoid(g)
     __shared__ float ig_s[ML_TB], fg_s[ML_TB], as[ML_TB], bs[ML_TB], em[ML_TB], mul_s[ML_TB], m_run;
     const int s = blockIdx.x, head = blockIdx.y, tid = threadIdx.x, n_threads = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, n_warps = n_threads >> 5;
     const int j0 = blockIdx.z * ML_VB, nv = min(ML_VB, V - j0);
-    const int jl = tid / ML_IG, ig = tid % ML_IG;
-    const bool col = jl <= nv, is_n = jl == nv;
+    const int cg = tid / ML_IG, ig = tid % ML_IG, c0 = cg * ML_CG;
+    const bool active = c0 <= nv;
     const int E = (D + ML_IG - 1) / ML_IG, i0 = ig * E;
+    auto chan = [&](int e) { return EXACT ? ((e >> 2) * ML_IG + ig) * 4 + (e & 3) : i0 + e; };   // key channel of entry e
     const float bi = i_bias[head], bf = f_bias[head];
     pdl_wait();
     const int slot = batch.seq_slot[s], row0 = batch.cu_q[s], row1 = batch.cu_q[s + 1];
@@ -86,12 +93,18 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
     float* ng = rec + (long long)H * D * V + (long long)head * D;
     float* mg = rec + (long long)H * D * V + (long long)H * D + head;
     if (tid == 0) m_run = *mg;
-    float S[EMAX];
+    float S[ML_CG][EMAX];
 #pragma unroll
-    for (int e = 0; e < EMAX; ++e) {
-        S[e] = 0.f;
-        if (col && e < E && i0 + e < D) S[e] = is_n ? ng[i0 + e] : Sg[(long long)(i0 + e) * V + j0 + jl];
-    }
+    for (int c = 0; c < ML_CG; ++c)
+#pragma unroll
+        for (int e = 0; e < EMAX; ++e) {
+            S[c][e] = 0.f;
+            if (active && e < E && chan(e) < D) {
+                if (c0 + c < nv) S[c][e] = Sg[(long long)chan(e) * V + j0 + c0 + c];
+                else if (c0 + c == nv) S[c][e] = ng[chan(e)];
+            }
+        }
+    for (int e = tid; e < ML_TB * ML_VW; e += n_threads) vs[e] = (e % ML_VW) == nv ? 1.0f : 0.f;   // columns that no load writes
     // A thread's first ML_PF turns of a tile's loads wait in registers while the tile before is worked on, so that the
     // loads' way to memory and back is hidden behind the recurrence; (token, column) of turn u follow from those of
     // turn 0 by additions.
@@ -137,7 +150,7 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
         const int nt = min(ML_TB, row1 - t0);
         __syncthreads();
         mlstm_gates(z, z_ld, i_col + head, f_col + head, bi, bf, cap, t0, nt, ig_s, fg_s, as, bs, em, &m_run);
-        {   // what waited in registers goes to shared memory; turns beyond ML_PF (few threads, wide heads) load now
+        {   // what waited in registers goes to shared memory; turns beyond ML_PF load now
             int e = tid;
 #pragma unroll
             for (int u = 0; u < ML_PF; ++u, e += n_threads)
@@ -145,6 +158,7 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
                     qs[e] = to_f<T>(rq[u]) * q_scale;
                     ks[e] = to_f<T>(rk[u]);
                 }
+#pragma unroll 4
             for (; e < nt * D; e += n_threads) {
                 const int tt = e / D, i = e - tt * D;
                 const long long at = (long long)(t0 + tt) * ld + head * D + i;
@@ -156,7 +170,7 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
 #pragma unroll
             for (int u = 0; u < ML_PF; ++u, e += n_threads) {
                 if (e < nt * nv) {
-                    vs[tt * ML_VB + c] = to_f<T>(rv[u]);
+                    vs[tt * ML_VW + c] = to_f<T>(rv[u]);
                     if (o_raw == nullptr) gs[tt * ML_VB + c] = 1.0f / (1.0f + expf(-to_f<T>(rg[u])));
                 }
                 tt += v_dt;
@@ -166,49 +180,97 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
                     ++tt;
                 }
             }
+#pragma unroll 4
             for (; e < nt * nv; e += n_threads) {
                 const int t2 = e / nv, c2 = e - t2 * nv;
                 const long long at = (long long)(t0 + t2) * ld + head * V + j0 + c2;
-                vs[t2 * ML_VB + c2] = to_f<T>(v[at]);
+                vs[t2 * ML_VW + c2] = to_f<T>(v[at]);
                 if (o_raw == nullptr) gs[t2 * ML_VB + c2] = 1.0f / (1.0f + expf(-to_f<T>(g[at])));
             }
         }
         __syncthreads();
         if (t0 + ML_TB < row1) fetch(t0 + ML_TB, min(ML_TB, row1 - t0 - ML_TB));
-#pragma unroll 4
-        for (int tt = 0; tt < nt; ++tt) {
-            const float vj = is_n ? 1.0f : (col ? vs[tt * ML_VB + jl] : 0.f);
-            const float a = as[tt], bv = bs[tt] * vj;
-            const float* qt = qs + tt * D + i0;
-            const float* kt = ks + tt * D + i0;
-            float o = 0.f;
+        {   // every thread walks the tokens (the shuffles want whole warps); a thread without columns reads the first ones
+            // and writes nothing
+            const int c0r = active ? c0 : 0;
+#pragma unroll 2
+            for (int tt = 0; tt < nt; ++tt) {
+                const float a = as[tt], b = bs[tt];
+                float bv[ML_CG], o[ML_CG];
 #pragma unroll
-            for (int e = 0; e < EMAX; ++e) {
-                if (e < E && i0 + e < D) {
-                    S[e] = fmaf(a, S[e], kt[e] * bv);
-                    o = fmaf(qt[e], S[e], o);
+                for (int c = 0; c < ML_CG; ++c) {
+                    bv[c] = b * vs[tt * ML_VW + c0r + c];
+                    o[c] = 0.f;
+                }
+                if (EXACT) {   // two entries of the state per instruction (fma.rn.f32x2): the time here is the instruction count
+                    constexpr int DC = ML_IG * EMAX;
+                    const float2 a2 = make_float2(a, a), zero = make_float2(0.f, 0.f);
+                    float2 o2[ML_CG];
+#pragma unroll
+                    for (int c = 0; c < ML_CG; ++c) o2[c] = zero;
+#pragma unroll
+                    for (int e = 0; e < EMAX; e += 4) {
+                        const int at = tt * DC + ((e >> 2) * ML_IG + ig) * 4;
+                        const float4 q4 = *reinterpret_cast<const float4*>(qs + at);
+                        const float4 k4 = *reinterpret_cast<const float4*>(ks + at);
+#pragma unroll
+                        for (int c = 0; c < ML_CG; ++c) {
+                            const float2 bv2 = make_float2(bv[c], bv[c]);
+                            float2 s01 = make_float2(S[c][e], S[c][e + 1]), s23 = make_float2(S[c][e + 2], S[c][e + 3]);
+                            s01 = fma_pair(a2, s01, fma_pair(make_float2(k4.x, k4.y), bv2, zero));
+                            s23 = fma_pair(a2, s23, fma_pair(make_float2(k4.z, k4.w), bv2, zero));
+                            o2[c] = fma_pair(make_float2(q4.x, q4.y), s01, o2[c]);
+                            o2[c] = fma_pair(make_float2(q4.z, q4.w), s23, o2[c]);
+                            S[c][e] = s01.x;
+                            S[c][e + 1] = s01.y;
+                            S[c][e + 2] = s23.x;
+                            S[c][e + 3] = s23.y;
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < ML_CG; ++c) o[c] = o2[c].x + o2[c].y;
+                } else {
+                    const float* qt = qs + tt * D + i0;
+                    const float* kt = ks + tt * D + i0;
+#pragma unroll
+                    for (int e = 0; e < EMAX; ++e) {
+                        if (e < E && i0 + e < D) {
+                            const float qe = qt[e], ke = kt[e];
+#pragma unroll
+                            for (int c = 0; c < ML_CG; ++c) {
+                                S[c][e] = fmaf(a, S[c][e], ke * bv[c]);
+                                o[c] = fmaf(qe, S[c][e], o[c]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < ML_CG; ++c) {
+                    o[c] += __shfl_xor_sync(0xffffffffu, o[c], 1);
+                    o[c] += __shfl_xor_sync(0xffffffffu, o[c], 2);
+                    o[c] += __shfl_xor_sync(0xffffffffu, o[c], 4);
+                }
+                if (ig == 0 && active) {
+#pragma unroll
+                    for (int c = 0; c < ML_CG; ++c) os[tt * ML_VW + c0 + c] = o[c];
                 }
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (ig == 0 && col) os[tt * (ML_VB + 1) + jl] = o;
         }
         __syncthreads();
         if (o_raw != nullptr) {
             for (int e = tid; e < nt * nv; e += n_threads) {
                 const int tt = e / nv, c = e - tt * nv;
-                const float den = fmaxf(fabsf(os[tt * (ML_VB + 1) + nv]), em[tt]) + 1e-6f;
-                o_raw[((long long)(t0 + tt) * H + head) * V + j0 + c] = os[tt * (ML_VB + 1) + c] / den;
+                const float den = fmaxf(fabsf(os[tt * ML_VW + nv]), em[tt]) + 1e-6f;
+                o_raw[((long long)(t0 + tt) * H + head) * V + j0 + c] = os[tt * ML_VW + c] / den;
             }
             continue;
         }
         for (int tt = warp; tt < nt; tt += n_warps) {   // the division and the head's root mean square, a warp per token
-            const float den = fmaxf(fabsf(os[tt * (ML_VB + 1) + nv]), em[tt]) + 1e-6f;
+            const float den = fmaxf(fabsf(os[tt * ML_VW + nv]), em[tt]) + 1e-6f;
             float ss = 0.f;
             for (int c = lane; c < nv; c += 32) {
-                const float h = os[tt * (ML_VB + 1) + c] / den;
-                os[tt * (ML_VB + 1) + c] = h;
+                const float h = os[tt * ML_VW + c] / den;
+                os[tt * ML_VW + c] = h;
                 ss = fmaf(h, h, ss);
             }
             ss = warp_sum(ss);
@@ -218,17 +280,19 @@ mlstm_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
         for (int e = tid; e < nt * nv; e += n_threads) {
             const int tt = e / nv, c = e - tt * nv;
             y[(long long)(t0 + tt) * y_ld + head * V + c] =
-                from_f<T>(os[tt * (ML_VB + 1) + c] * mul_s[tt] * norm_w[head * V + c] * gs[tt * ML_VB + c]);
+                from_f<T>(os[tt * ML_VW + c] * mul_s[tt] * norm_w[head * V + c] * gs[tt * ML_VB + c]);
         }
     }
     __syncthreads();
 #pragma unroll
-    for (int e = 0; e < EMAX; ++e) {
-        if (col && e < E && i0 + e < D) {
-            if (!is_n) Sg[(long long)(i0 + e) * V + j0 + jl] = S[e];
-            else if (blockIdx.z == 0) ng[i0 + e] = S[e];
+    for (int c = 0; c < ML_CG; ++c)
+#pragma unroll
+        for (int e = 0; e < EMAX; ++e) {
+            if (active && e < E && chan(e) < D) {
+                if (c0 + c < nv) Sg[(long long)chan(e) * V + j0 + c0 + c] = S[c][e];
+                else if (c0 + c == nv && blockIdx.z == 0) ng[chan(e)] = S[c][e];
+            }
         }
-    }
     if (tid == 0 && blockIdx.z == 0) *mg = m_run;
 }
 
@@ -344,26 +408,29 @@ int sb_mlstm_scan(int dtype, const void* q, const void* k, const void* v, const 
                       (bf*)y, y_ld);
         SB_LAUNCH_CHECK();
     }
-    const size_t smem = (size_t)(ML_TB * (2 * D + 3 * ML_VB + 1)) * sizeof(float);
+    const size_t smem = (size_t)(ML_TB * (2 * D + 2 * ML_VW + ML_VB)) * sizeof(float);
     dim3 grid(batch.n_seqs, H, chunks);
-    const int threads = ((min(V, ML_VB) + 1) * ML_IG + 31) / 32 * 32;
+    const int threads = (((min(V, ML_VB) + 1 + ML_CG - 1) / ML_CG) * ML_IG + 31) / 32 * 32;
     float* raw = chunks > 1 ? o_raw : nullptr;
-#define SB_ML(T, EMAX)                                                                                                               \
+#define SB_ML(T, EMAX, EXACT)                                                                                                        \
     do {                                                                                                                             \
         if (smem > 48 * 1024) {                                                                                                      \
-            const cudaError_t err = cudaFuncSetAttribute(mlstm_scan_kernel<T, EMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
-                                                         (int)smem);                                                                 \
+            const cudaError_t err = cudaFuncSetAttribute(mlstm_scan_kernel<T, EMAX, EXACT>,                                          \
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                    \
             if (err != cudaSuccess) return (int)err;                                                                                 \
         }                                                                                                                            \
-        sb_launch(mlstm_scan_kernel<T, EMAX>, grid, threads, smem, stream, (const T*)q, (const T*)k, (const T*)v, (const T*)g, ld, z, \
-                  z_ld, i_col, f_col, i_bias, f_bias, cap, norm_w, eps, q_scale, out_scale, state, state_stride, batch, H, D, V,     \
-                  (T*)y, y_ld, raw);                                                                                                 \
+        sb_launch(mlstm_scan_kernel<T, EMAX, EXACT>, grid, threads, smem, stream, (const T*)q, (const T*)k, (const T*)v, (const T*)g, \
+                  ld, z, z_ld, i_col, f_col, i_bias, f_bias, cap, norm_w, eps, q_scale, out_scale, state, state_stride, batch, H, D, \
+                  V, (T*)y, y_ld, raw);                                                                                              \
     } while (0)
-#define SB_ML_SIZES(T)                  \
-    do {                                \
-        if (D <= 32) SB_ML(T, 4);       \
-        else if (D <= 64) SB_ML(T, 8);  \
-        else SB_ML(T, 16);              \
+#define SB_ML_SIZES(T)                            \
+    do {                                          \
+        if (D == 32) SB_ML(T, 4, true);           \
+        else if (D == 64) SB_ML(T, 8, true);      \
+        else if (D == 128) SB_ML(T, 16, true);    \
+        else if (D <= 32) SB_ML(T, 4, false);     \
+        else if (D <= 64) SB_ML(T, 8, false);     \
+        else SB_ML(T, 16, false);                 \
     } while (0)
     if (dtype == SB_F32) SB_ML_SIZES(float);
     else SB_ML_SIZES(bf);
