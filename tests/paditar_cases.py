@@ -5,7 +5,7 @@ to the last layer, of one pass, and none; rotations over part of a head, over th
 heads than query heads, as many, and a single head; convolutions of 1, 2, 3 and 5 taps and none; a query temperature
 that steps at every position, every 5, every 64, and none; matrix memories with keys wider than 128 columns and values
 wider than 64 (the recurrence kernel's other paths), caps from 1.5 to 30; scales of the two sides that are equal, 1 and
-far apart; a layer without feed-forward; widths that are no multiples of 8.
+far apart; a layer without feed-forward; widths that are no multiples of 8 or of 4, and odd head sizes.
 """
 
 from __future__ import annotations
@@ -73,8 +73,14 @@ CASES = {
     # one pass (the loop's vector is still added), the loop reaches the last layer, five taps
     "D": _model(64, 32, 1e-5, (1, 2, 1), [_with(_attention(2, 2, 8, 8, 0.6, rot=(10000.0, 2)), 16),
                                           _with(_parallel((2, 2, 8, 5, (2.0, 3), None), (4, 8, 8, 5.0), 1.0, 0.7), 48)]),
+    # a width that is no multiple of 4, odd head sizes everywhere (rows that no 16-byte read fits), an odd vocabulary, the loop
+    # over all layers, eight taps, twelve query heads on one key head
+    "E": _model(131, 30, 1e-6, (0, 3, 2), [
+        _with(_parallel((3, 1, 7, 8, (0.7, 2), 0.5), (3, 5, 3, 4.0), 0.9, 1.1), 14),
+        _with(_attention(3, 1, 5, 7, 0.35, rot=(50.0, 2)), 22),
+        _with(_parallel((12, 1, 4, 2, None, None), (1, 9, 65, 9.0), 1.0, 0.3), None)]),
 }
-SEEDS = {"A": 35, "B": 36, "C": 37, "D": 38}
+SEEDS = {"A": 35, "B": 36, "C": 37, "D": 38, "E": 39}
 
 
 def config(name):
