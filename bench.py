@@ -473,8 +473,8 @@ def _paditar_raw(width, attention, left, right, ff, vocab=32000):
     two_maps = {"type": "attention", "mixer": dict(attention, scale=attention["dim"] ** -0.5, diff=0.5,
                                                    rot={"base": 500000.0, "dims": attention["dim"] // 2})}
     pair = {"type": "parallel", "mixer": {"left": dict(left, vdim=left["dim"], scale=left["dim"] ** -0.5, conv=4,
-                                                       q_temp={"coef": 0.3, "every": 64}),
-                                          "right": dict(right, gate_cap=15.0), "left_scale": 1.0, "right_scale": 0.5}}
+                                                       q_temp={"coef": 0.2, "every": 64}),
+                                          "right": dict(right, gate_cap=15.0), "left_scale": 1.0, "right_scale": 0.6}}
     mlp = {"kind": "dense", "ff": ff}
     entries = [dict(kind, mlp=mlp) for kind in (pair, two_maps, pair, two_maps)]
     return {"architecture": "Paditar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "loop": {"start": 0, "stop": 2, "times": 2},

@@ -2,7 +2,8 @@
 //
 //   conv_qk_store   u = projection + bias; y_t = sum_j w[:, j] * u_(t - taps + 1 + j) per channel (zeros before the
 //                   sequence's start; inputs before the step from the sequence's record); per head the RMS norm of y
-//                   with a weight of the head's size; queries times 1 + coef * ln(floor((pos + 1) / every) + 1).
+//                   with a weight of the head's size (none without weights); queries times
+//                   1 + coef * ln(floor((pos + 1) / every) + 1).
 //                   The normed keys go to the key rows of the cache, the keys as they leave the convolution (before
 //                   the norm) to its value rows: the values of this attention are its keys.
 //   head_gate       out = a * sigmoid(z[:, head]) * scale: one gate per head and row.
@@ -62,10 +63,11 @@ __global__ void conv_qk_store_kernel(const T* __restrict__ q, long long q_ld, co
             ss = fmaf(y, y, ss);
         }
         ss = block_sum(ss, red);
-        const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+        const bool normed = q_norm != nullptr;      // without norm weights queries and keys pass as they are
+        const float rstd = normed ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
         if (is_q) {
             T* dst = q_out + ((long long)row * H + h) * D;
-            for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = from_f<T>(ys[c] * rstd * q_norm[c] * temp);
+            for (int c = threadIdx.x; c < D; c += blockDim.x) dst[c] = from_f<T>(ys[c] * rstd * (normed ? q_norm[c] : 1.0f) * temp);
         } else {
             const long long tok = flex_token(p, slot, pos, h);
             if (tok < 0) {
@@ -75,7 +77,7 @@ __global__ void conv_qk_store_kernel(const T* __restrict__ q, long long q_ld, co
             T* kd = (T*)p.k + tok * D;
             T* vd = (T*)p.v + flex_value_token(p, tok, h) * p.v_row;
             for (int c = threadIdx.x; c < D; c += blockDim.x) {
-                kd[c] = from_f<T>(ys[c] * rstd * k_norm[c]);
+                kd[c] = from_f<T>(ys[c] * rstd * (normed ? k_norm[c] : 1.0f));
                 vd[c] = from_f<T>(ys[c]);
             }
         }
@@ -127,7 +129,8 @@ int sb_conv_qk_store(int dtype, const void* q, long long q_ld, const void* k, lo
                      int* status, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     const bool conv = q_conv != nullptr;
-    if ((q_conv == nullptr) != (k_conv == nullptr) || (conv && (taps < 1 || (taps > 1 && state == nullptr))) || p.v == nullptr
+    if ((q_conv == nullptr) != (k_conv == nullptr) || (q_norm == nullptr) != (k_norm == nullptr)
+        || (conv && (taps < 1 || (taps > 1 && state == nullptr))) || p.v == nullptr
         || p.v_dim != p.k_dim)
         return (int)cudaErrorInvalidValue;
     const int D = p.k_dim, units = H + p.n_kv_heads;

@@ -1102,8 +1102,8 @@ class Ops:
         convolution per channel (``q_conv`` [heads * D, taps]; ``state`` [slots, taps - 1, (heads + kv heads) * D] holds each
         sequence's last biased projections and is brought up to date), normed per head with the weights of D values, the
         queries times 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1).  The normed keys go to the cache's key rows,
-        the keys before the norm to its value rows; the queries come back as [rows, heads, D].  Biases and convolutions may
-        be None; ``temp_every`` 0 leaves the queries as they are."""
+        the keys before the norm to its value rows; the queries come back as [rows, heads, D].  Biases, convolutions and the
+        norm weights may be None; ``temp_every`` 0 leaves the queries as they are."""
         g = layer_cache.group
         G, D = g.request.num_kv_heads, g.request.head_dim
         rows = q.shape[0]
@@ -1122,8 +1122,8 @@ class Ops:
         for t, n in ((q_bias, n_heads * D), (k_bias, G * D), (q_norm, D), (k_norm, D)):
             if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
                 raise KernelError("conv_qk_store: biases and norm weights are 32-bit")
-        if q_norm is None or k_norm is None:
-            raise KernelError("conv_qk_store: queries and keys are normed")
+        if (q_norm is None) != (k_norm is None):
+            raise KernelError("conv_qk_store: queries and keys are normed together or not at all")
         out = torch.empty((rows, n_heads, D), dtype=q.dtype, device=q.device)
         p = self._flex(layer_cache)
         self._check(self.lib.sb_conv_qk_store(_code(q.dtype), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(q_bias), _ptr(k_bias),

@@ -67,10 +67,10 @@ class KeyValueAttention:
         self.o_bias = (f32("o_bias") * self.out_scale).contiguous() if spec.bias else None
         self.q_conv = f32("q_conv") if spec.taps else None
         self.k_conv = f32("k_conv") if spec.taps else None
+        self.q_norm = self.k_norm = None
+        self.eps = 0.0
         if spec.qk_norm_eps is not None:
             self.q_norm, self.k_norm, self.eps = f32("q_norm"), f32("k_norm"), float(spec.qk_norm_eps)
-        else:   # no norm: a weight of ones would still divide by the root mean square, so it is an error to ask the kernel
-            raise ValueError("this attention norms its queries and keys; a spec without qk_norm_eps is not built")
         self.sink = torch.zeros(H, dtype=torch.float32, device=dev) if spec.unit_sink else None
 
     def cache_request(self):

@@ -279,7 +279,7 @@ class EmulatedOps:
         yq, yk = y[:, :n_heads * D].reshape(rows, n_heads, D), y[:, n_heads * D:].reshape(rows, G, D)
 
         def unit(t, w):
-            return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.float()
+            return t if w is None else t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.float()
 
         slots, pos = self._positions(ctx)
         qn = unit(yq, q_norm)

@@ -60,7 +60,7 @@ CASES = {
         _with(_parallel((2, 1, 32, 2, (1.0, 1), 0.3), (2, 40, 72, 15.0), 1.0, 1.0), 40)]),
     # sizes the tensor-core kernels take; two passes from the first layer on; a temperature that steps once a page
     "B": _model(300, 128, 1e-6, (0, 2, 2), [
-        _with(_parallel((4, 1, 64, 4, (0.3, 64), None), (2, 64, 64, 12.0), 0.8, 1.3), 256),
+        _with(_parallel((4, 1, 64, 4, (0.25, 64), None), (2, 64, 64, 11.0), 0.8, 1.3), 256),
         _with(_attention(8, 2, 32, 64, 0.5, rot=(1000000.0, 16)), 192),
         _with(_attention(2, 1, 64, 128, 0.8, rot=(10000.0, 64), scale=0.2), 64)]),
     # no loop, no rotation, single heads, one tap and no convolution at all, no temperature, widths that are no multiples

@@ -215,7 +215,7 @@ def test_the_gate_is_taken_element_by_element():
 
 # ---- attention whose values are its keys -----------------------------------------------------------------------
 
-def kva_spec(H, G, D, taps=4, temp=(0.3, 64), scale=None, width=80):
+def kva_spec(H, G, D, taps=4, temp=(0.25, 64), scale=None, width=80):
     return KeyValueAttentionSpec(hidden_size=width, num_heads=H, num_kv_heads=G, head_dim=D, scale=D ** -0.5 if scale is None else scale,
                                  bias=True, taps=taps or 0, qk_norm_eps=EPS, temp_coef=temp[0] if temp else 0.0,
                                  temp_every=temp[1] if temp else 0, unit_sink=True, head_gate=True)
@@ -246,12 +246,12 @@ def plain_kva(h, w, s):
 
 KVA_SIZES = [
     dict(H=4, G=2, D=24, taps=3, temp=(0.5, 5)),                 # the general kernel
-    dict(H=4, G=1, D=64, taps=4, temp=(0.3, 64)),                # sizes the tensor-core kernels take; the temperature steps once a page
+    dict(H=4, G=1, D=64, taps=4, temp=(0.25, 64)),                # sizes the tensor-core kernels take; the temperature steps once a page
     dict(H=8, G=2, D=128, taps=2, temp=(1.0, 1), scale=0.05),    # a step at every position
     dict(H=1, G=1, D=20, taps=1, temp=None),                     # one tap keeps no record
     dict(H=3, G=3, D=6, taps=None, temp=(0.1, 7)),               # no convolution at all
     dict(H=2, G=2, D=8, taps=5, temp=(2.0, 3)),
-    dict(H=16, G=4, D=64, taps=4, temp=(0.3, 64)),
+    dict(H=16, G=4, D=64, taps=3, temp=(0.4, 32)),
 ]
 
 
@@ -267,6 +267,27 @@ def test_key_value_attention_alone(mode, sizes):
     want = plain_kva(h, w, spec)
     for cuts in cuttings(n):
         close(run_part(rt, part, h, cuts), want, mode, f"cut {cuts[:3]}..")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_key_value_attention_without_its_norm(mode):
+    """The spec's norm is an option: without it queries and keys go on as they are.  The expected output is put together
+    here from the plain helpers (temperature, softmax with a 1 in its denominator), since the plain mixer always norms."""
+    import dataclasses
+    rt = runtime(mode)
+    spec = dataclasses.replace(kva_spec(H=2, G=1, D=16, taps=None, temp=(0.5, 4), scale=0.3, width=32), qk_norm_eps=None)
+    w = kva_weights(dataclasses.replace(spec, qk_norm_eps=EPS), 33)
+    w.pop("q.norm"), w.pop("k.norm")
+    n = 40
+    h = rand((n, 32), 11)
+    # the plain attention by hand, from the plain helpers, without the unit norms
+    q = (h.double() @ w["q"].double().T + w["q.b"].double()).reshape(n, 2, 16) * plain.query_temperature(n, 0.5, 4)[:, None, None]
+    k = (h.double() @ w["k"].double().T + w["k.b"].double()).reshape(n, 1, 16)
+    gate = torch.sigmoid(h.double() @ w["g"].double().T)
+    heads = [plain.softmax_attention(q[:, i], k[:, 0], k[:, 0], 0.3, extra_one=True) * gate[:, i:i + 1] for i in range(2)]
+    want = torch.cat(heads, dim=-1) @ w["o"].double().T + w["o.b"].double()
+    for cuts in ([n], [n - 9] + [1] * 9):
+        close(run_part(rt, part_of(rt, spec, w), h, cuts), want, mode, f"cut {cuts[:3]}..")
 
 
 def standout(spec, n, at, seed, strength=5.0):
@@ -298,7 +319,7 @@ def standout(spec, n, at, seed, strength=5.0):
 @pytest.mark.parametrize("n, at", [(330, 0), (330, 1), (200, 63), (200, 64), (200, 65), (330, 127), (330, 128), (700, 5), (150, 149)])
 def test_a_key_that_stands_out_far_back_and_at_page_borders(mode, n, at):
     rt = runtime(mode)
-    spec = kva_spec(H=4, G=2, D=64, taps=2, temp=(0.3, 64), scale=0.6)
+    spec = kva_spec(H=4, G=2, D=64, taps=2, temp=(0.25, 64), scale=0.6)
     h, w = standout(spec, n, at, 50)
     want = plain_kva(h, w, spec)
     if 0 < at < n - 1:    # the test can tell: with an ordinary row in the key's place the later outputs move by a good part of their size
@@ -400,7 +421,7 @@ def plain_mem(h, w, s):
 
 MEM_SIZES = [
     dict(H=3, D=16, V=24, cap=8.0),
-    dict(H=2, D=64, V=64, cap=12.0),
+    dict(H=2, D=64, V=64, cap=11.0),
     dict(H=4, D=128, V=128, cap=15.0),      # a head's columns shared out over two blocks
     dict(H=1, D=136, V=12, cap=1.5),        # keys wider than the registers hold: the state stays in memory
     dict(H=2, D=10, V=130, cap=30.0),       # three blocks of columns, the last one nearly empty
